@@ -1,0 +1,151 @@
+/*
+ * b200norm.h -- C ABI of libb200norm.so: LayerNorm / RMSNorm forward and backward for
+ * NVIDIA B200 (sm_100a), written as hand-tuned CUDA kernels.
+ *
+ * The library stands where the host wrappers of TritonHub's Normalization package stand:
+ *
+ *   b200norm_ln_fwd   replaces  _layernorm_fwd   TritonHub/Normalization/layernorm.py:48-87
+ *                               (+ kernel        TritonHub/Normalization/layernorm.py:14-46)
+ *   b200norm_ln_bwd   replaces  _layernorm_bwd   TritonHub/Normalization/layernorm.py:155-209
+ *                               (+ kernel        TritonHub/Normalization/layernorm.py:94-153,
+ *                                 + the `_dw.sum(0).to(dtype)` finish at :207-208)
+ *   b200norm_rms_fwd  replaces  _rmsnorm_fwd     TritonHub/Normalization/rmsnorm.py:40-70
+ *   b200norm_rms_bwd  replaces  _rmsnorm_bwd     TritonHub/Normalization/rmsnorm.py:124-167
+ *   the launch table behind them replaces get_cuda_autotune_config(block_keys=None)
+ *                                                TritonHub/autotune.py:61-65
+ *
+ * Conventions shared by every entry point
+ *   - Rows are the flattened leading dimensions: x is (M, N) with unit column stride and a
+ *     row stride given in ELEMENTS (>= N).  y, dy and dx likewise.
+ *   - All pointers are device pointers of the CUDA device that is current on the calling
+ *     thread; the caller owns every buffer.  The library only enqueues work on `stream`
+ *     (a cudaStream_t passed as void*; NULL = legacy default stream).  It never
+ *     synchronises, never changes the current device and, after the first call on a device,
+ *     never allocates.  The first call on a device caches the device's SM count, the
+ *     occupancy of each kernel and maps a small pinned status word; make that call before
+ *     any stream capture.
+ *   - Arithmetic is fp32 whatever the storage type (the reference promotes every load to
+ *     fp32, layernorm.py:31,41); results are rounded once on store.
+ *   - Return value: B200NORM_OK or one of the error codes below.  Nothing throws or aborts.
+ *     b200norm_last_error() returns a thread-local description of the last failure.
+ *   - Re-entrant and thread-safe (autograd calls backward from its own worker thread).
+ */
+#ifndef B200NORM_H_
+#define B200NORM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200NORM_VERSION 100 /* major*10000 + minor*100 + patch */
+
+#if defined(__GNUC__)
+#define B200NORM_API __attribute__((visibility("default")))
+#else
+#define B200NORM_API
+#endif
+
+/* Storage types of x / y / dy / dx (io_dtype) and of weight / bias / dweight / dbias (w_dtype). */
+enum b200norm_dtype {
+  B200NORM_F32 = 0,
+  B200NORM_F16 = 1,
+  B200NORM_BF16 = 2,
+  B200NORM_F64 = 3 /* accepted like the reference does: loaded, then computed in fp32 */
+};
+
+enum b200norm_status {
+  B200NORM_OK = 0,
+  B200NORM_ERR_ARG = 1,         /* null pointer, bad stride, negative size, bad enum, small workspace */
+  B200NORM_ERR_UNSUPPORTED = 2, /* row wider than 64 KB (the reference's limit, layernorm.py:69-72) */
+  B200NORM_ERR_CUDA = 3,        /* a CUDA runtime call failed; text in b200norm_last_error() */
+  B200NORM_ERR_TIMEOUT = 4      /* a bounded device-side wait gave up (see b200norm_device_status) */
+};
+
+/* Library version (B200NORM_VERSION of the build). */
+B200NORM_API int b200norm_version(void);
+
+/* SM count of the current device and the largest number of dweight/dbias partial rows a
+ * backward call can write there.  Cached per device; replaces the per-call
+ * torch.cuda.get_device_properties() of layernorm.py:182. */
+B200NORM_API int b200norm_query(int* sm_count, int* max_partials);
+
+/* Text for the last non-OK status returned on this thread ("" if none). */
+B200NORM_API const char* b200norm_last_error(void);
+
+/* Sticky per-device status word written by kernels whose bounded waits (mbarrier waits on
+ * bulk copies) ran out: 0 = never happened.  Reading it does not synchronise; call it after
+ * the stream has been synchronised.  `clear` != 0 resets it. */
+B200NORM_API int b200norm_device_status(int clear);
+
+/* Bytes of scratch a backward call needs for its fp32 dweight/dbias partial rows
+ * (replaces the `_dw`/`_db` (sm_count, N) buffers of layernorm.py:183-184).
+ * `row_shards` is the number of equal row groups whose sums are kept apart (1 unless the
+ * caller wants results that do not depend on how many GPUs the rows are spread over). */
+B200NORM_API size_t b200norm_bwd_workspace_bytes(int64_t M, int64_t N, int io_dtype, int row_shards);
+
+/*
+ * LayerNorm forward (layernorm.py:14-87): per row
+ *   mean = sum(x)/N; var = sum((x-mean)^2)/N; rstd = 1/sqrt(var+eps);
+ *   y = (x-mean)*rstd [*w] [+b]
+ * w, b may each be NULL (HAS_WEIGHT / HAS_BIAS false).  mean and rstd are (M,) fp32 outputs
+ * saved for backward.
+ */
+B200NORM_API int b200norm_ln_fwd(const void* x, int64_t x_row_stride, const void* w, const void* b, void* y,
+                    int64_t y_row_stride, float* mean, float* rstd, int64_t M, int64_t N, float eps,
+                    int io_dtype, int w_dtype, void* stream);
+
+/*
+ * RMSNorm forward (rmsnorm.py:14-70): rstd = 1/sqrt(sum(x^2)/N + eps); y = x*rstd [*w].
+ */
+B200NORM_API int b200norm_rms_fwd(const void* x, int64_t x_row_stride, const void* w, void* y, int64_t y_row_stride,
+                     float* rstd, int64_t M, int64_t N, float eps, int io_dtype, int w_dtype,
+                     void* stream);
+
+/*
+ * LayerNorm backward (layernorm.py:94-209): per row, with xhat = (x-mean)*rstd, wdy = w*dy
+ * (w = 1 when NULL):
+ *   c1 = sum(xhat*wdy)/N; c2 = sum(wdy)/N; dx = (wdy - (xhat*c1 + c2))*rstd
+ *   dw = sum_rows(dy*xhat); db = sum_rows(dy)
+ * dw / db: (N,) outputs in w_dtype, or NULL to skip that gradient.
+ * group_sums: optional fp32 output (row_shards, 2, N): the dweight (slot 0) and dbias (slot 1)
+ *   sums of each row shard before the final add and cast -- what a multi-GPU caller
+ *   exchanges.  NULL if not wanted.  When given, dw/db are still written if non-NULL.
+ * row_shards >= 1 splits the M rows into that many equal groups (M % row_shards == 0) whose
+ *   partial sums are formed separately and then added left to right, so that a run over one
+ *   shard per GPU followed by b200norm_finalize_dwdb gives bit-identical dw/db.
+ * workspace: at least b200norm_bwd_workspace_bytes(M, N, io_dtype, row_shards) bytes,
+ *   256-byte aligned; contents undefined on entry and on exit.
+ */
+B200NORM_API int b200norm_ln_bwd(const void* x, int64_t x_row_stride, const void* dy, int64_t dy_row_stride,
+                    const void* w, const float* mean, const float* rstd, void* dx,
+                    int64_t dx_row_stride, void* dw, void* db, float* group_sums, int row_shards,
+                    void* workspace, size_t workspace_bytes, int64_t M, int64_t N, int io_dtype,
+                    int w_dtype, void* stream);
+
+/*
+ * RMSNorm backward (rmsnorm.py:77-167): xhat = x*rstd; c1 = sum(xhat*wdy)/N;
+ *   dx = (wdy - xhat*c1)*rstd; dw = sum_rows(dy*xhat).
+ * group_sums, when given, is (row_shards, 1, N) fp32.
+ */
+B200NORM_API int b200norm_rms_bwd(const void* x, int64_t x_row_stride, const void* dy, int64_t dy_row_stride,
+                     const void* w, const float* rstd, void* dx, int64_t dx_row_stride, void* dw,
+                     float* group_sums, int row_shards, void* workspace, size_t workspace_bytes,
+                     int64_t M, int64_t N, int io_dtype, int w_dtype, void* stream);
+
+/*
+ * Finish dweight/dbias from gathered shard sums: out[k][n] = sum_{g=0..groups-1} in[g][k][n]
+ * added left to right in fp32, then cast to w_dtype.  `slots` is 2 for LayerNorm (dw, db) and
+ * 1 for RMSNorm.  This is the step after an all-gather of every rank's group_sums; it has no
+ * counterpart in the single-GPU reference beyond the `.sum(0).to(dtype)` of layernorm.py:207-208.
+ * dw / db may be NULL.
+ */
+B200NORM_API int b200norm_finalize_dwdb(const float* group_sums, int groups, int slots, void* dw, void* db, int64_t N,
+                           int w_dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200NORM_H_ */

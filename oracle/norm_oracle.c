@@ -1,0 +1,213 @@
+/*
+ * norm_oracle.c -- CPU restatement of TritonHub's LayerNorm / RMSNorm forward and backward.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This file is the checker the CUDA kernels are compared with and
+ * the CPU baseline that the benchmark times; no product code path may call it.
+ *
+ * Every function follows the reference's algorithm step by step (file:line cited at each
+ * function).  Storage types are handled by the caller: inputs arrive as fp32 arrays holding
+ * values already rounded to the storage type (widening fp16 / bf16 to fp32 is exact; fp64
+ * inputs are narrowed first, which is what the reference's `.to(tl.float32)` does,
+ * layernorm.py:31), and outputs leave as un-rounded fp32 for the caller to round once.
+ *
+ * Row sums are marked `omp simd reduction` (compiled with -fopenmp-simd, no OpenMP runtime):
+ * like the reference's tl.sum, their association order is not the sequential one.
+ *
+ * acc64 = 0: all arithmetic in fp32, like the reference's kernels.
+ * acc64 = 1: the same formulas evaluated in fp64 ("truth", used to scale tolerances).
+ *
+ * Pinned against (tests/test_oracle.py): outputs of the reference's own Triton kernel
+ * bodies executed by Triton's interpreter (tests/golden/, made by tests/golden/make_golden.py)
+ * and torch.nn.functional.layer_norm / rms_norm on CPU, the comparator the reference's
+ * UnitTests use (UnitTests/Normalization/layernorm_unittest.py:17,37,46).
+ */
+#include <math.h>
+#include <pthread.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#define API __attribute__((visibility("default")))
+
+/* ---- a minimal parallel-for over [0, n) on `g_threads` POSIX threads -------------------- */
+static int g_threads = 1;
+API void oracle_set_threads(int n) { g_threads = n < 1 ? 1 : (n > 256 ? 256 : n); }
+API int oracle_get_threads(void) { return g_threads; }
+
+typedef void (*range_fn)(int64_t begin, int64_t end, void* ctx);
+typedef struct { range_fn fn; void* ctx; int64_t begin, end; } range_job;
+static void* range_thread(void* a) {
+  range_job* j = (range_job*)a;
+  j->fn(j->begin, j->end, j->ctx);
+  return NULL;
+}
+static void parallel_for(int64_t n, range_fn fn, void* ctx) {
+  int t = g_threads;
+  if (t > n) t = (int)(n > 0 ? n : 1);
+  if (t <= 1) { fn(0, n, ctx); return; }
+  pthread_t tid[256];
+  range_job job[256];
+  const int64_t chunk = (n + t - 1) / t;
+  for (int i = 0; i < t; ++i) {
+    job[i].fn = fn; job[i].ctx = ctx;
+    job[i].begin = i * chunk;
+    job[i].end = (i + 1) * chunk > n ? n : (i + 1) * chunk;
+    if (job[i].begin > n) job[i].begin = n;
+    pthread_create(&tid[i], NULL, range_thread, &job[i]);
+  }
+  for (int i = 0; i < t; ++i) pthread_join(tid[i], NULL);
+}
+
+/* One row of _layernorm_kernel_fwd (TritonHub/Normalization/layernorm.py:27-46) or, with
+ * rms != 0, of _rmsnorm_kernel_fwd (TritonHub/Normalization/rmsnorm.py:24-38). */
+#define ROW_FWD(ACC)                                                                     \
+  do {                                                                                   \
+    ACC mean = 0;                                                                        \
+    if (!rms) {                                                                          \
+      ACC s = 0;                                                                         \
+      _Pragma("omp simd reduction(+ : s)")                                               \
+      for (int64_t c = 0; c < N; ++c) s += (ACC)xr[c];                                   \
+      mean = s / (ACC)N;                                  /* layernorm.py:32 */          \
+    }                                                                                    \
+    ACC q = 0;                                                                           \
+    _Pragma("omp simd reduction(+ : q)")                                                 \
+    for (int64_t c = 0; c < N; ++c) {                                                    \
+      ACC d = (ACC)xr[c] - mean;                          /* layernorm.py:34 */          \
+      q += d * d;                                                                        \
+    }                                                                                    \
+    ACC var = q / (ACC)N;                                 /* layernorm.py:35, rmsnorm.py:30 */ \
+    ACC rs = (ACC)1 / (ACC)sqrt((double)(var + (ACC)eps)); /* layernorm.py:36 */          \
+    if (sizeof(ACC) == 4) rs = (ACC)(1.0f / sqrtf((float)var + eps));                    \
+    if (mean_out) mean_out[r] = (float)mean;              /* layernorm.py:33 */          \
+    rstd_out[r] = (float)rs;                              /* layernorm.py:37 */          \
+    for (int64_t c = 0; c < N; ++c) {                                                    \
+      ACC yv = ((ACC)xr[c] - mean) * rs;                  /* layernorm.py:38 */          \
+      if (w) yv = yv * (ACC)w[c];                         /* layernorm.py:40-42 */       \
+      if (b) yv = yv + (ACC)b[c];                         /* layernorm.py:43-45 */       \
+      yr[c] = (float)yv;                                                                 \
+    }                                                                                    \
+  } while (0)
+
+/* Forward over M rows (host glue of _layernorm_fwd, layernorm.py:48-87: one program per row).
+ * x: (M, N) with row stride xs; y: (M, N) contiguous; mean_out may be NULL for RMSNorm. */
+typedef struct {
+  const float *x, *w, *b;
+  float *y, *mean_out, *rstd_out;
+  int64_t xs, N;
+  float eps;
+  int rms, acc64;
+} fwd_ctx;
+
+static void fwd_rows(int64_t begin, int64_t end, void* vctx) {
+  const fwd_ctx* k = (const fwd_ctx*)vctx;
+  const float *w = k->w, *b = k->b;
+  float *mean_out = k->mean_out, *rstd_out = k->rstd_out;
+  const int64_t N = k->N;
+  const float eps = k->eps;
+  const int rms = k->rms;
+  for (int64_t r = begin; r < end; ++r) {
+    const float* xr = k->x + r * k->xs;
+    float* yr = k->y + r * N;
+    if (k->acc64) ROW_FWD(double);
+    else ROW_FWD(float);
+  }
+}
+
+API void oracle_norm_fwd(const float* x, int64_t xs, const float* w, const float* b, float* y, float* mean_out,
+                         float* rstd_out, int64_t M, int64_t N, float eps, int rms, int acc64) {
+  fwd_ctx k = {x, w, b, y, mean_out, rstd_out, xs, N, eps, rms, acc64};
+  parallel_for(M, fwd_rows, &k);
+}
+
+/* One program of _layernorm_kernel_bwd (layernorm.py:113-153) / _rmsnorm_kernel_bwd
+ * (rmsnorm.py:92-122): rows [row_start, row_end), dweight / dbias accumulated across them. */
+#define PROG_BWD(ACC)                                                                    \
+  do {                                                                                   \
+    ACC* dwp = (ACC*)calloc((size_t)N, sizeof(ACC));                                     \
+    ACC* dbp = (ACC*)calloc((size_t)N, sizeof(ACC));                                     \
+    ACC* xh = (ACC*)malloc((size_t)N * sizeof(ACC));                                     \
+    ACC* wdy = (ACC*)malloc((size_t)N * sizeof(ACC));                                    \
+    for (int64_t r = row_start; r < row_end; ++r) {                                      \
+      const float* xr = x + r * xs;                                                      \
+      const float* gr = dy + r * dys;                                                    \
+      float* dxr = dx + r * N;                                                           \
+      ACC mu = rms ? (ACC)0 : (ACC)mean[r];                                              \
+      ACC rs = (ACC)rstd[r];                                                             \
+      ACC s1 = 0, s2 = 0;                                                                \
+      _Pragma("omp simd reduction(+ : s1, s2)")                                          \
+      for (int64_t c = 0; c < N; ++c) {                                                  \
+        xh[c] = ((ACC)xr[c] - mu) * rs;                   /* layernorm.py:132 */         \
+        wdy[c] = w ? (ACC)w[c] * (ACC)gr[c] : (ACC)gr[c]; /* layernorm.py:135,141 */     \
+        dwp[c] += (ACC)gr[c] * xh[c];                     /* layernorm.py:136 */         \
+        dbp[c] += (ACC)gr[c];                             /* layernorm.py:145 */         \
+        s1 += xh[c] * wdy[c];                                                            \
+        s2 += wdy[c];                                                                    \
+      }                                                                                  \
+      ACC c1 = s1 / (ACC)N;                               /* layernorm.py:137 */         \
+      ACC c2 = rms ? (ACC)0 : s2 / (ACC)N;                /* layernorm.py:138 */         \
+      for (int64_t c = 0; c < N; ++c)                                                    \
+        dxr[c] = (float)((wdy[c] - (xh[c] * c1 + c2)) * rs); /* layernorm.py:139 */      \
+    }                                                                                    \
+    for (int64_t c = 0; c < N; ++c) {                     /* layernorm.py:150-153 */     \
+      dw_part[(size_t)prog * N + c] = (double)dwp[c];                                    \
+      db_part[(size_t)prog * N + c] = (double)dbp[c];                                    \
+    }                                                                                    \
+    free(dwp); free(dbp); free(xh); free(wdy);                                           \
+  } while (0)
+
+/* Backward over M rows with the reference's work split (host glue of _layernorm_bwd,
+ * layernorm.py:155-209): `programs` programs (sm_count there) of ceil(M/programs) consecutive
+ * rows each, one fp32 partial row per program, then the column sum of the partial rows
+ * (`_dw.sum(0)`, layernorm.py:207-208) -- left to right here, in the accumulation type.
+ * dw / db (N,) may be NULL.  The cast to the parameter dtype is the caller's. */
+typedef struct {
+  const float *x, *dy, *w, *mean, *rstd;
+  float* dx;
+  double *dw_part, *db_part;
+  int64_t xs, dys, M, N, rows_per_program;
+  int rms, acc64;
+} bwd_ctx;
+
+static void bwd_programs(int64_t begin, int64_t end, void* vctx) {
+  const bwd_ctx* k = (const bwd_ctx*)vctx;
+  const float *x = k->x, *dy = k->dy, *w = k->w, *mean = k->mean, *rstd = k->rstd;
+  float* dx = k->dx;
+  double *dw_part = k->dw_part, *db_part = k->db_part;
+  const int64_t xs = k->xs, dys = k->dys, N = k->N;
+  const int rms = k->rms;
+  for (int64_t prog = begin; prog < end; ++prog) {
+    const int64_t row_start = prog * k->rows_per_program;
+    int64_t row_end = row_start + k->rows_per_program;
+    if (row_end > k->M) row_end = k->M;                            /* layernorm.py:126 */
+    if (k->acc64) PROG_BWD(double);
+    else PROG_BWD(float);
+  }
+}
+
+API int oracle_norm_bwd(const float* x, int64_t xs, const float* dy, int64_t dys, const float* w, const float* mean,
+                        const float* rstd, float* dx, float* dw, float* db, int64_t M, int64_t N, int programs,
+                        int rms, int acc64) {
+  if (programs < 1) return 1;
+  double* dw_part = (double*)calloc((size_t)programs * N, sizeof(double));
+  double* db_part = (double*)calloc((size_t)programs * N, sizeof(double));
+  if (!dw_part || !db_part) return 2;
+  const int64_t rows_per_program = (M + programs - 1) / programs; /* layernorm.py:185 */
+  bwd_ctx k = {x, dy, w, mean, rstd, dx, dw_part, db_part, xs, dys, M, N, rows_per_program, rms, acc64};
+  parallel_for(programs, bwd_programs, &k);
+  for (int64_t c = 0; c < N; ++c) {
+    if (acc64) {
+      double a = 0, bsum = 0;
+      for (int p = 0; p < programs; ++p) { a += dw_part[(size_t)p * N + c]; bsum += db_part[(size_t)p * N + c]; }
+      if (dw) dw[c] = (float)a;
+      if (db) db[c] = (float)bsum;
+    } else {
+      float a = 0, bsum = 0;
+      for (int p = 0; p < programs; ++p) { a += (float)dw_part[(size_t)p * N + c]; bsum += (float)db_part[(size_t)p * N + c]; }
+      if (dw) dw[c] = a;
+      if (db) db[c] = bsum;
+    }
+  }
+  free(dw_part);
+  free(db_part);
+  return 0;
+}

@@ -1,0 +1,127 @@
+"""numpy front end of the CPU oracle (oracle/norm_oracle.c).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke check and by the benchmark's CPU
+baseline -- never by the product package.
+
+The C side restates the reference's kernels (TritonHub/Normalization/layernorm.py:14-46,
+94-153; rmsnorm.py:14-38,77-122) and host glue (layernorm.py:48-87,155-209).  This module
+adds what the reference gets from torch dtypes: rounding to the storage type on the way in and
+on the way out (`round_to`), and the parity metric the tests use.
+"""
+from __future__ import annotations
+
+import ctypes
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+_HERE = Path(__file__).resolve().parent
+_LIB_PATH = _HERE / "liboracle.so"
+_lib = None
+
+_f32p = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
+
+
+def build() -> Path:
+    """Compile liboracle.so with the Makefile beside this file (gcc only)."""
+    subprocess.run(["make", "-C", str(_HERE), "liboracle.so"], check=True, capture_output=True)
+    return _LIB_PATH
+
+
+def _load():
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            build()
+        lib = ctypes.CDLL(str(_LIB_PATH))
+        vp, i64, i32, f32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float
+        lib.oracle_norm_fwd.restype = None
+        lib.oracle_norm_fwd.argtypes = [vp, i64, vp, vp, vp, vp, vp, i64, i64, f32, i32, i32]
+        lib.oracle_norm_bwd.restype = i32
+        lib.oracle_norm_bwd.argtypes = [vp, i64, vp, i64, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32]
+        lib.oracle_set_threads.argtypes = [i32]
+        lib.oracle_get_threads.restype = i32
+        _lib = lib
+    return _lib
+
+
+def set_threads(n: int) -> None:
+    """Number of POSIX threads the oracle's row loops use (1 = the scalar port)."""
+    _load().oracle_set_threads(int(n))
+
+
+def round_to(a: np.ndarray, dtype: str) -> np.ndarray:
+    """Round values to storage type `dtype` ('fp32', 'fp16', 'bf16', 'fp64') and return them
+    widened to float32 (float64 for 'fp64'), i.e. what a kernel sees after its load."""
+    if dtype == "fp64":
+        return np.asarray(a, dtype=np.float64)
+    a32 = np.ascontiguousarray(a, dtype=np.float32)
+    if dtype == "fp32":
+        return a32
+    if dtype == "fp16":
+        return a32.astype(np.float16).astype(np.float32)
+    if dtype == "bf16":  # round to nearest even on the upper 16 bits
+        u = a32.view(np.uint32).astype(np.uint64)
+        rounded = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
+        out = rounded.astype(np.uint32).view(np.float32).reshape(a32.shape).copy()
+        nan = np.isnan(a32)
+        out[nan] = np.nan
+        return out
+    raise ValueError(dtype)
+
+
+def _as_f32(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data
+
+
+def norm_fwd(x, w, b, eps, *, rms=False, acc64=False):
+    """Forward.  x: (M, N) array of storage-rounded values.  Returns (y, mean, rstd) as fp32,
+    y not yet rounded to the storage type; mean is None for RMSNorm."""
+    x = _as_f32(x)
+    M, N = x.shape
+    w, b = _as_f32(w), (None if rms else _as_f32(b))
+    y = np.empty((M, N), np.float32)
+    mean = None if rms else np.empty((M,), np.float32)
+    rstd = np.empty((M,), np.float32)
+    _load().oracle_norm_fwd(_p(x), N, _p(w), _p(b), _p(y), _p(mean), _p(rstd), M, N, float(eps), int(rms),
+                            int(acc64))
+    return y, mean, rstd
+
+
+def norm_bwd(x, dy, w, mean, rstd, *, rms=False, programs=148, acc64=False):
+    """Backward with the reference's `programs`-way row split (sm_count there).  Returns
+    (dx, dw, db) as fp32 before the cast to the storage / parameter type; db is None for
+    RMSNorm."""
+    x, dy = _as_f32(x), _as_f32(dy)
+    M, N = x.shape
+    w = _as_f32(w)
+    mean = None if rms else _as_f32(mean)
+    rstd = _as_f32(rstd)
+    dx = np.empty((M, N), np.float32)
+    dw = np.empty((N,), np.float32)
+    db = None if rms else np.empty((N,), np.float32)
+    rc = _load().oracle_norm_bwd(_p(x), N, _p(dy), N, _p(w), _p(mean), _p(rstd), _p(dx), _p(dw), _p(db), M, N,
+                                 int(programs), int(rms), int(acc64))
+    if rc != 0:
+        raise RuntimeError(f"oracle_norm_bwd failed ({rc})")
+    return dx, dw, db
+
+
+def rel_err(a, ref) -> float:
+    """The parity metric: max|a - ref| / max|ref| over the whole tensor."""
+    a = np.asarray(a, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    if ref.size == 0:
+        return 0.0
+    scale = float(np.max(np.abs(ref)))
+    err = float(np.max(np.abs(a - ref)))
+    return err / scale if scale > 0 else err
+
+
+# Parity bars: relative to the tensor's largest magnitude.
+TOL = {"fp32": 1e-5, "fp64": 1e-5, "fp16": 1e-2, "bf16": 1e-2}

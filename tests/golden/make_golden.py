@@ -1,0 +1,108 @@
+"""Generate the golden vectors in this directory from the reference implementation.
+
+Run once, where the reference checkout is available (it is not needed to *use* the vectors):
+
+    TRITON_INTERPRET=1 python tests/golden/make_golden.py /path/to/Triton-Hub
+
+The reference has no stored vectors of its own and its wrappers need a GPU, so this script
+executes the reference's four Triton kernel bodies (TritonHub/Normalization/layernorm.py:14-46,
+94-153; rmsnorm.py:14-38,77-122) on CPU through Triton's interpreter, restating only the host
+glue around them (allocation, BLOCK_SIZE, rows_per_program and the final `.sum(0).to(dtype)`,
+layernorm.py:63-72,176-208) with PROGRAMS standing in for the GPU's SM count.  Inputs are
+seeded; every case is written to <name>.npz together with what the reference produced.
+16-bit tensors are stored as fp16 arrays or bf16 bit patterns (uint16) to keep files small.
+"""
+import math
+import os
+import sys
+from pathlib import Path
+
+os.environ.setdefault("TRITON_INTERPRET", "1")
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+PROGRAMS = 4  # stands in for sm_count (layernorm.py:182)
+
+# name, op, dtype, M-shape, N, eps, x mean, x std, has_weight, has_bias
+CASES = [
+    ("c1_ln_fp32_2x100x128", "ln", torch.float32, (2, 100), 128, 1e-6, 0.0, 1.0, True, True),
+    ("rms_bf16_8x4096", "rms", torch.bfloat16, (8,), 4096, 1e-6, 0.0, 1.0, True, False),
+    ("ln_fp16_6x5120_mean3", "ln", torch.float16, (6,), 5120, 1e-5, 3.0, 2.0, True, True),
+    ("ln_bf16_3x16384", "ln", torch.bfloat16, (3,), 16384, 1e-6, 0.0, 1.0, True, True),
+    ("ln_bf16_8x4096", "ln", torch.bfloat16, (8,), 4096, 1e-6, 0.0, 1.0, True, True),
+    ("ln_fp32_7x100_nobias", "ln", torch.float32, (7,), 100, 1e-5, 0.0, 1.0, True, False),
+    ("rms_fp32_5x33_noweight", "rms", torch.float32, (5,), 33, 1e-5, 0.0, 1.0, False, False),
+    ("ln_fp64_4x64", "ln", torch.float64, (4,), 64, 1e-5, 0.0, 1.0, True, True),
+    ("ln_fp16_5x256_noaffine", "ln", torch.float16, (5,), 256, 1e-5, 0.0, 1.0, False, False),
+    ("rms_fp16_9x1000", "rms", torch.float16, (9,), 1000, 1e-5, 0.0, 1.0, True, False),
+]
+
+
+def next_pow2(n):
+    return 1 << (n - 1).bit_length()
+
+
+def store(t):
+    """torch tensor -> (suffix, numpy array) in a compact, exact form."""
+    if t.dtype == torch.bfloat16:
+        return "__bf16bits", t.view(torch.int16).numpy().view(np.uint16)
+    return "", t.numpy()
+
+
+def run_case(L, R, name, op, dtype, batch, N, eps, mu, sigma, has_w, has_b):
+    g = torch.Generator().manual_seed(0)
+    M = int(np.prod(batch))
+    x = (torch.randn(M, N, generator=g) * sigma + mu).to(dtype)
+    dy = torch.randn(M, N, generator=g).to(dtype)
+    w = (1 + 0.1 * torch.randn(N, generator=g)).to(dtype) if has_w else None
+    b = (0.1 * torch.randn(N, generator=g)).to(dtype) if has_b else None
+    BLOCK = min(65536 // x.element_size(), next_pow2(N))
+    y = torch.empty_like(x)
+    rstd = torch.empty(M, dtype=torch.float32)
+    dx = torch.empty_like(x)
+    rpp = math.ceil(M / PROGRAMS)
+    dwp = torch.empty(PROGRAMS, N, dtype=torch.float32) if has_w else None
+    out = {}
+    if op == "ln":
+        mean = torch.empty(M, dtype=torch.float32)
+        L._layernorm_kernel_fwd.fn[(M,)](x, x.stride(0), y, y.stride(0), w, b, mean, rstd, eps, N,
+                                         BLOCK_SIZE=BLOCK, HAS_WEIGHT=has_w, HAS_BIAS=has_b)
+        dbp = torch.empty(PROGRAMS, N, dtype=torch.float32) if has_b else None
+        L._layernorm_kernel_bwd.fn[(PROGRAMS,)](x, x.stride(0), dy, dy.stride(0), dx, dx.stride(0), w, b, dwp, dbp,
+                                                mean, rstd, eps, M, N, rpp, BLOCK_SIZE=BLOCK, HAS_WEIGHT=has_w,
+                                                HAS_BIAS=has_b)
+        out["mean"] = mean.numpy()
+        if has_b:
+            k, v = store(dbp.sum(0).to(b.dtype))
+            out["db" + k] = v
+    else:
+        R._rmsnorm_kernel_fwd.fn[(M,)](x, x.stride(0), y, y.stride(0), w, rstd, eps, N, BLOCK_SIZE=BLOCK,
+                                       HAS_WEIGHT=has_w)
+        R._rmsnorm_kernel_bwd.fn[(PROGRAMS,)](x, x.stride(0), dy, dy.stride(0), dx, dx.stride(0), w, dwp, rstd, eps,
+                                              M, N, rpp, BLOCK_SIZE=BLOCK, HAS_WEIGHT=has_w)
+    out["rstd"] = rstd.numpy()
+    for key, t in (("x", x), ("dy", dy), ("w", w), ("b", b), ("y", y), ("dx", dx)):
+        if t is not None:
+            k, v = store(t)
+            out[key + k] = v
+    if has_w:
+        k, v = store(dwp.sum(0).to(w.dtype))
+        out["dw" + k] = v
+    out["meta"] = np.array([op, str(dtype).replace("torch.", ""), str(eps), str(PROGRAMS),
+                            "x".join(map(str, batch))])
+    np.savez_compressed(HERE / f"{name}.npz", **out)
+    print(name, "ok", sum(v.nbytes for v in out.values()) // 1024, "KiB raw")
+
+
+def main():
+    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    sys.path.insert(0, ref)
+    from TritonHub.Normalization import layernorm as L
+    from TritonHub.Normalization import rmsnorm as R
+    for case in CASES:
+        run_case(L, R, *case)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,249 @@
+"""Parity of the CUDA kernels, called through the C ABI (ctypes) exactly as the modules call
+them, with the CPU oracle and the golden vectors.
+
+Bars (north star): max|a-ref| <= tol * max|ref| per tensor with tol = 1e-5 for fp32 storage
+and 1e-2 for fp16 / bf16, on y, dx, dweight and dbias.  `ref` is the oracle evaluated in
+fp64 and rounded to the storage type, or the golden output of the reference's own kernels.
+"""
+import numpy as np
+import pytest
+import torch
+
+from helpers import (GOLDEN, TOL, TORCH_DTYPE, assert_parity, load_golden, make_inputs, oracle_all, to_numpy,
+                     to_torch)
+
+pytestmark = pytest.mark.gpu
+
+import b200norm
+from b200norm import LayerNorm, RMSNorm, _lib
+from b200norm import functional as Fn
+
+DEV = "cuda:0"
+
+
+def run_ours(x, dy, w, b, eps, *, rms, dtype, wdtype=None, row_shards=1):
+    """numpy in -> our kernels through the functional wrappers -> numpy out."""
+    wdtype = wdtype or dtype
+    xt, dyt = to_torch(x, dtype, DEV), to_torch(dy, dtype, DEV)
+    wt, bt = to_torch(w, wdtype, DEV), to_torch(b, wdtype, DEV)
+    if rms:
+        y, rstd = Fn._rmsnorm_fwd(xt, wt, eps)
+        dx, dw = Fn._rmsnorm_bwd(xt, dyt, wt, rstd, eps, row_shards=row_shards)
+        mean, db = None, None
+    else:
+        y, mean, rstd = Fn._layernorm_fwd(xt, wt, bt, eps)
+        dx, dw, db = Fn._layernorm_bwd(xt, dyt, wt, bt, mean, rstd, eps, row_shards=row_shards)
+    torch.cuda.synchronize()
+    return {k: to_numpy(v) for k, v in dict(y=y, mean=mean, rstd=rstd, dx=dx, dw=dw, db=db).items()}
+
+
+def check_against_oracle(x, dy, w, b, eps, *, rms, dtype, wdtype=None, row_shards=1, label=""):
+    got = run_ours(x, dy, w, b, eps, rms=rms, dtype=dtype, wdtype=wdtype, row_shards=row_shards)
+    ref = oracle_all(x, dy, w, b, eps, rms=rms, dtype=dtype, programs=8, acc64=True)
+    if wdtype is not None and wdtype != dtype:
+        # parameter gradients are rounded to the parameter type, not the activation type
+        from oracle import oracle as O
+        y, mean, rstd = O.norm_fwd(x, w, None if rms else b, eps, rms=rms, acc64=True)
+        _, dw, db = O.norm_bwd(x, dy, w, mean, rstd, rms=rms, programs=8, acc64=True)
+        ref["dw"] = O.round_to(dw, wdtype) if w is not None else None
+        ref["db"] = O.round_to(db, wdtype) if (b is not None and not rms) else None
+    tol = TOL[dtype]
+    for key in ("y", "dx", "dw", "db"):
+        if ref[key] is None:
+            assert got[key] is None, f"{label}{key} should be None"
+            continue
+        assert_parity(got[key], ref[key], tol, f"{label}{key}")
+    assert_parity(got["rstd"], ref["rstd"], 1e-5, f"{label}rstd")
+    if not rms:
+        assert_parity(got["mean"], ref["mean"], 1e-5, f"{label}mean")
+    return got
+
+
+def test_library_is_loaded_and_device_is_a_b200_class_gpu():
+    lib = _lib.load()
+    sm, mp = np.zeros(1, np.int32), np.zeros(1, np.int32)
+    import ctypes
+    a, c = ctypes.c_int(), ctypes.c_int()
+    with torch.cuda.device(0):
+        _lib.check(lib.b200norm_query(ctypes.byref(a), ctypes.byref(c)))
+    assert a.value == torch.cuda.get_device_properties(0).multi_processor_count
+    assert c.value >= a.value
+
+
+@pytest.mark.parametrize("name", GOLDEN)
+def test_golden_vectors(name):
+    g = load_golden(name)
+    rms = g["op"] == "rms"
+    got = run_ours(g["x"], g["dy"], g["w"], g["b"], g["eps"], rms=rms, dtype=g["dtype"])
+    tol = TOL[g["dtype"]]
+    for key in ("y", "dx", "dw", "db"):
+        if g[key] is None:
+            continue
+        assert_parity(got[key], g[key], tol, f"{name}:{key}")
+    assert_parity(got["rstd"], g["rstd"], 1e-5, f"{name}:rstd")
+    if not rms:
+        assert_parity(got["mean"], g["mean"], 1e-5, f"{name}:mean")
+
+
+DIMS = [1, 3, 8, 33, 100, 128, 256, 1000, 1024, 2048, 3000, 4096, 5120, 8192, 12288, 16384]
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "fp16", "bf16", "fp64"])
+@pytest.mark.parametrize("rms", [False, True])
+def test_dim_sweep_vs_oracle(dtype, rms):
+    limit = 65536 // {"fp32": 4, "fp16": 2, "bf16": 2, "fp64": 8}[dtype]
+    dims = [d for d in DIMS + [24576, 32768] if d <= limit]
+    for N in dims:
+        M = 37 if N <= 4096 else 11
+        x, dy, w, b = make_inputs(M, N, dtype, seed=N, has_b=not rms)
+        check_against_oracle(x, dy, w, b, 1e-5, rms=rms, dtype=dtype, label=f"N={N} ")
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_every_small_dim(dtype):
+    """Every N from 1 to 257 at a few row counts: exercises each packet-count predicate and the
+    any-alignment kernels."""
+    for N in range(1, 258):
+        M = 1 + N % 5
+        x, dy, w, b = make_inputs(M, N, dtype, seed=1000 + N)
+        check_against_oracle(x, dy, w, b, 1e-5, rms=bool(N % 2), dtype=dtype, label=f"N={N} M={M} ")
+
+
+@pytest.mark.parametrize("has_w,has_b", [(True, True), (True, False), (False, False), (False, True)])
+def test_optional_weight_and_bias(has_w, has_b):
+    for dtype, N in (("fp32", 384), ("bf16", 4096), ("fp16", 77)):
+        x, dy, w, b = make_inputs(19, N, dtype, has_w=has_w, has_b=has_b)
+        check_against_oracle(x, dy, w, b, 1e-6, rms=False, dtype=dtype)
+    x, dy, w, _ = make_inputs(19, 512, "bf16", has_w=has_w, has_b=False)
+    check_against_oracle(x, dy, w, None, 1e-6, rms=True, dtype="bf16")
+
+
+@pytest.mark.parametrize("M", [1, 2, 147, 149, 593, 4099])
+def test_row_counts_around_the_grid_size(M):
+    x, dy, w, b = make_inputs(M, 1024, "bf16", seed=M)
+    check_against_oracle(x, dy, w, b, 1e-5, rms=False, dtype="bf16")
+    check_against_oracle(x, dy, w, None, 1e-5, rms=True, dtype="bf16")
+
+
+def test_fp32_parameters_with_16bit_activations():
+    for dtype in ("bf16", "fp16"):
+        x, dy, _, _ = make_inputs(64, 2048, dtype)
+        _, _, w, b = make_inputs(1, 2048, "fp32", seed=5)
+        check_against_oracle(x, dy, w, b, 1e-5, rms=False, dtype=dtype, wdtype="fp32")
+
+
+def test_row_strided_and_non_contiguous_inputs():
+    torch.manual_seed(0)
+    N = 512
+    big = torch.randn(40, 2 * N, device=DEV, dtype=torch.float16)
+    x = big[:, :N]                      # row stride 2N, unit column stride: used without a copy
+    assert x.stride() == (2 * N, 1)
+    dy = torch.randn(40, N, device=DEV, dtype=torch.float16)
+    w = torch.randn(N, device=DEV, dtype=torch.float16)
+    b = torch.randn(N, device=DEV, dtype=torch.float16)
+    y, mean, rstd = Fn._layernorm_fwd(x, w, b, 1e-5)
+    yc, meanc, rstdc = Fn._layernorm_fwd(x.contiguous(), w, b, 1e-5)
+    assert torch.equal(y, yc) and torch.equal(mean, meanc) and torch.equal(rstd, rstdc)
+    dx, dw, db = Fn._layernorm_bwd(x, dy, w, b, mean, rstd, 1e-5)
+    dxc, dwc, dbc = Fn._layernorm_bwd(x.contiguous(), dy, w, b, mean, rstd, 1e-5)
+    assert torch.equal(dx, dxc) and torch.equal(dw, dwc) and torch.equal(db, dbc)
+    # unaligned view (odd element offset) goes through the any-alignment kernels
+    flat = torch.randn(40 * N + 1, device=DEV, dtype=torch.float16)
+    xu = flat[1:].view(40, N)
+    yu, _, _ = Fn._layernorm_fwd(xu, w, b, 1e-5)
+    yuc, _, _ = Fn._layernorm_fwd(xu.clone(), w, b, 1e-5)
+    torch.testing.assert_close(yu, yuc, rtol=1e-2, atol=1e-2)
+    # non-unit last stride is made contiguous, as the reference does (layernorm.py:49-50)
+    xt = torch.randn(N, 24, device=DEV, dtype=torch.float16).t()
+    y1, _, _ = Fn._layernorm_fwd(xt, w, b, 1e-5)
+    y2, _, _ = Fn._layernorm_fwd(xt.contiguous(), w, b, 1e-5)
+    assert torch.equal(y1, y2)
+
+
+def test_batch_shape_is_restored():
+    m = LayerNorm(128, eps=1e-6, device=DEV, dtype=torch.float32)
+    x = torch.randn(2, 100, 128, device=DEV, requires_grad=True)
+    y = m(x)
+    assert y.shape == x.shape and y.is_contiguous()
+    y.backward(torch.randn_like(y))
+    assert x.grad.shape == x.shape and m.weight.grad.shape == (128,) and m.bias.grad.shape == (128,)
+
+
+def test_run_to_run_bitwise_determinism():
+    x, dy, w, b = make_inputs(3000, 4096, "bf16")
+    a = run_ours(x, dy, w, b, 1e-6, rms=False, dtype="bf16")
+    c = run_ours(x, dy, w, b, 1e-6, rms=False, dtype="bf16")
+    for k in a:
+        assert np.array_equal(a[k], c[k]), k
+
+
+@pytest.mark.parametrize("rms", [False, True])
+def test_row_shards_equal_separate_launches_bit_for_bit(rms):
+    """One launch over 8 row shards == 8 launches over one shard each + finalize: the property
+    that makes a row-sharded multi-GPU run reproduce the single-GPU dweight / dbias exactly."""
+    M, N, S = 8 * 600, 4096, 8
+    x, dy, w, b = make_inputs(M, N, "bf16", has_b=not rms)
+    xt, dyt, wt = (to_torch(a, "bf16", DEV) for a in (x, dy, w))
+    bt = to_torch(b, "bf16", DEV)
+    if rms:
+        y, rstd = Fn._rmsnorm_fwd(xt, wt, 1e-6)
+        dx, dw, gs = Fn._rmsnorm_bwd(xt, dyt, wt, rstd, 1e-6, row_shards=S, group_sums=True)
+        db = None
+    else:
+        y, mean, rstd = Fn._layernorm_fwd(xt, wt, bt, 1e-6)
+        dx, dw, db, gs = Fn._layernorm_bwd(xt, dyt, wt, bt, mean, rstd, 1e-6, row_shards=S, group_sums=True)
+    parts, dxs = [], []
+    R = M // S
+    for s in range(S):
+        sl = slice(s * R, (s + 1) * R)
+        if rms:
+            dxi, _, gi = Fn._rmsnorm_bwd(xt[sl], dyt[sl], wt, rstd[sl], 1e-6, group_sums=True)
+        else:
+            dxi, _, _, gi = Fn._layernorm_bwd(xt[sl], dyt[sl], wt, bt, mean[sl], rstd[sl], 1e-6, group_sums=True)
+        parts.append(gi)
+        dxs.append(dxi)
+    gathered = torch.cat(parts, 0).contiguous()
+    assert torch.equal(gathered, gs)
+    outs = Fn.finalize_dwdb(gathered, torch.bfloat16)
+    assert torch.equal(outs[0], dw)
+    if not rms:
+        assert torch.equal(outs[1], db)
+    assert torch.equal(torch.cat(dxs, 0), dx)
+
+
+def test_outputs_do_not_write_out_of_bounds():
+    """Canaries either side of y / dx / mean / rstd survive (the row-strided output path)."""
+    N, M = 1000, 53
+    lib = _lib.load()
+    x = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    pad = 64
+    ybuf = torch.full((M * N + 2 * pad,), 7.0, device=DEV, dtype=torch.bfloat16)
+    sbuf = torch.full((2, M + 2 * pad), 7.0, device=DEV, dtype=torch.float32)
+    y = ybuf[pad:pad + M * N]
+    _lib.check(lib.b200norm_ln_fwd(x.data_ptr(), N, w.data_ptr(), None, y.data_ptr(), N,
+                                   sbuf[0, pad:].data_ptr(), sbuf[1, pad:].data_ptr(), M, N, 1e-5, _lib.BF16,
+                                   _lib.BF16, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert torch.all(ybuf[:pad] == 7) and torch.all(ybuf[pad + M * N:] == 7)
+    assert torch.all(sbuf[:, :pad] == 7) and torch.all(sbuf[:, pad + M:] == 7)
+    ref = torch.nn.functional.layer_norm(x.float(), (N,), w.float(), None, 1e-5)
+    assert_parity(to_numpy(y.view(M, N)), to_numpy(ref), 1e-2, "y")
+
+
+def test_small_workspace_is_rejected():
+    lib = _lib.load()
+    M, N = 64, 256
+    x = torch.randn(M, N, device=DEV)
+    stat = torch.ones(M, device=DEV)
+    dx = torch.empty_like(x)
+    dw = torch.empty(N, device=DEV)
+    ws = torch.empty(256, dtype=torch.uint8, device=DEV)
+    rc = lib.b200norm_rms_bwd(x.data_ptr(), N, x.data_ptr(), N, None, stat.data_ptr(), dx.data_ptr(), N,
+                              dw.data_ptr(), None, 1, ws.data_ptr(), 256, M, N, _lib.F32, _lib.F32, None)
+    assert rc == _lib.ERR_ARG and b"workspace" in lib.b200norm_last_error()
+
+
+def test_device_status_word_is_clean():
+    with torch.cuda.device(0):
+        assert _lib.load().b200norm_device_status(0) == 0

@@ -1,0 +1,8 @@
+"""b200norm: LayerNorm / RMSNorm forward + backward for NVIDIA B200 as hand-written sm_100a
+CUDA kernels behind TritonHub's module and autograd.Function interface."""
+from .functional import (_layernorm_bwd, _layernorm_fwd, _rmsnorm_bwd, _rmsnorm_fwd, finalize_dwdb, layernorm,
+                         rmsnorm)
+from .modules import LayerNorm, RMSNorm
+
+__all__ = ['LayerNorm', 'RMSNorm', 'layernorm', 'rmsnorm', 'finalize_dwdb']
+__version__ = '0.1.0'

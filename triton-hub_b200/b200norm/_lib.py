@@ -1,0 +1,66 @@
+"""ctypes binding of libb200norm.so (C ABI declared in include/b200norm.h).
+
+There is no fallback: if the shared library has not been built, or a call returns a non-zero
+status, a RuntimeError is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libb200norm.so"
+
+# Status codes of enum b200norm_status.
+OK, ERR_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT = range(5)
+
+# Storage type codes of enum b200norm_dtype.
+F32, F16, BF16, F64 = range(4)
+
+_c = ctypes
+_vp, _i64, _int, _f32, _sz = _c.c_void_p, _c.c_int64, _c.c_int, _c.c_float, _c.c_size_t
+
+# name -> (restype, argtypes): every symbol include/b200norm.h declares.
+SIGNATURES = {
+    "b200norm_version": (_int, []),
+    "b200norm_query": (_int, [_c.POINTER(_int), _c.POINTER(_int)]),
+    "b200norm_last_error": (_c.c_char_p, []),
+    "b200norm_device_status": (_int, [_int]),
+    "b200norm_bwd_workspace_bytes": (_sz, [_i64, _i64, _int, _int]),
+    "b200norm_ln_fwd": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _f32, _int, _int, _vp]),
+    "b200norm_rms_fwd": (_int, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _i64, _f32, _int, _int, _vp]),
+    "b200norm_ln_bwd": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _int, _vp, _sz,
+                               _i64, _i64, _int, _int, _vp]),
+    "b200norm_rms_bwd": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _int, _vp, _sz, _i64, _i64,
+                                _int, _int, _vp]),
+    "b200norm_finalize_dwdb": (_int, [_vp, _int, _int, _vp, _vp, _i64, _int, _vp]),
+}
+
+_lock = threading.Lock()
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load libb200norm.so once and set every prototype.  Raises if it is not built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            if not LIB_PATH.exists():
+                raise RuntimeError(
+                    f"{LIB_PATH} is missing: build it with `python {LIB_PATH.parent / 'build.py'}` "
+                    "(needs nvcc; there is no Triton, PyTorch or CPU fallback for these kernels)")
+            lib = ctypes.CDLL(str(LIB_PATH))
+            for name, (res, args) in SIGNATURES.items():
+                fn = getattr(lib, name)
+                fn.restype, fn.argtypes = res, args
+            _lib = lib
+    return _lib
+
+
+def check(status: int) -> None:
+    """Turn a non-zero status into the RuntimeError the reference's wrappers would raise."""
+    if status != OK:
+        msg = load().b200norm_last_error().decode() or f"b200norm status {status}"
+        raise RuntimeError(msg)

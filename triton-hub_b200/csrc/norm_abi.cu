@@ -1,0 +1,360 @@
+// C ABI of libb200norm.so (declared in include/b200norm.h): argument checks, the fixed launch
+// table and the kernel launches.  Nothing here synchronises or, after a device's first call,
+// allocates.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+
+#include "b200norm.h"
+#include "norm_bwd.cuh"
+#include "norm_colreduce.cuh"
+#include "norm_fwd.cuh"
+#include "norm_table.h"
+
+namespace b200norm {
+namespace {
+
+constexpr int kMaxDevices = 64;
+constexpr int64_t kMaxRowBytes = 65536;  // the reference's limit (layernorm.py:69-72)
+constexpr int kLN = 0, kRMS = 1;
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+struct DeviceState {
+  std::once_flag once;
+  cudaError_t init_err = cudaSuccess;
+  int sm_count = 0;
+  int* status_host = nullptr;  // pinned, mapped: kernels report a timed-out wait here
+  int* status_dev = nullptr;
+  std::mutex mu;
+  std::unordered_map<unsigned long long, int> occupancy;  // (kernel, dyn smem) -> CTAs per SM
+};
+DeviceState g_dev[kMaxDevices];
+
+// Per-device set-up, run by the first call on each device.
+int device_state(DeviceState** out) {
+  int d = -1;
+  cudaError_t e = cudaGetDevice(&d);
+  if (e != cudaSuccess) return fail(B200NORM_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (d < 0 || d >= kMaxDevices) return fail(B200NORM_ERR_CUDA, "device index %d out of range", d);
+  DeviceState& s = g_dev[d];
+  std::call_once(s.once, [&]() {
+    s.init_err = cudaDeviceGetAttribute(&s.sm_count, cudaDevAttrMultiProcessorCount, d);
+    if (s.init_err != cudaSuccess) return;
+    s.init_err = cudaHostAlloc(reinterpret_cast<void**>(&s.status_host), 64, cudaHostAllocMapped);
+    if (s.init_err != cudaSuccess) return;
+    std::memset(s.status_host, 0, 64);
+    s.init_err = cudaHostGetDevicePointer(reinterpret_cast<void**>(&s.status_dev), s.status_host, 0);
+  });
+  if (s.init_err != cudaSuccess)
+    return fail(B200NORM_ERR_CUDA, "device set-up: %s", cudaGetErrorString(s.init_err));
+  *out = &s;
+  return B200NORM_OK;
+}
+
+// Resident CTAs per SM of `fn` at this block size and dynamic shared memory; cached.
+int occupancy(DeviceState& s, const void* fn, int threads, size_t smem, int* out) {
+  const unsigned long long key =
+      (reinterpret_cast<unsigned long long>(fn) * 0x9E3779B97F4A7C15ull) ^ (unsigned long long)smem;
+  std::lock_guard<std::mutex> lock(s.mu);
+  auto it = s.occupancy.find(key);
+  if (it != s.occupancy.end()) {
+    *out = it->second;
+    return B200NORM_OK;
+  }
+  cudaError_t e;
+  if (smem > 48 * 1024) {
+    e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess)
+      return fail(B200NORM_ERR_CUDA, "cudaFuncSetAttribute(%zu B): %s", smem, cudaGetErrorString(e));
+  }
+  int n = 0;
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, fn, threads, smem);
+  if (e != cudaSuccess) return fail(B200NORM_ERR_CUDA, "occupancy query: %s", cudaGetErrorString(e));
+  if (n < 1) return fail(B200NORM_ERR_CUDA, "kernel does not fit on an SM (%d threads, %zu B smem)", threads, smem);
+  s.occupancy.emplace(key, n);
+  *out = n;
+  return B200NORM_OK;
+}
+
+const DTypeKernels* kernels_for(int dtype) {
+  switch (dtype) {
+    case B200NORM_F32: return kernels_f32();
+    case B200NORM_F16: return kernels_f16();
+    case B200NORM_BF16: return kernels_bf16();
+    case B200NORM_F64: return kernels_f64();
+    default: return nullptr;
+  }
+}
+
+bool valid_dtype(int d) { return d >= B200NORM_F32 && d <= B200NORM_F64; }
+
+bool aligned16(const void* p, int64_t stride_elems, int es) {
+  return (reinterpret_cast<uintptr_t>(p) & 15u) == 0 && ((stride_elems * es) & 15) == 0;
+}
+
+// First table entry whose capacity covers a row of V packets, or null.
+const PacketKernel* pick(const PacketKernel* tab, int n, int64_t V) {
+  for (int i = 0; i < n; ++i)
+    if (tab[i].capacity() >= V) return &tab[i];
+  return nullptr;
+}
+
+int launch(const void* fn, dim3 grid, dim3 block, size_t smem, void* params, cudaStream_t stream) {
+  void* args[1] = {params};
+  cudaError_t e = cudaLaunchKernel(fn, grid, block, args, smem, stream);
+  if (e != cudaSuccess) return fail(B200NORM_ERR_CUDA, "kernel launch: %s", cudaGetErrorString(e));
+  return B200NORM_OK;
+}
+
+int check_common(int64_t M, int64_t N, int io_dtype, int w_dtype) {
+  if (!valid_dtype(io_dtype) || !valid_dtype(w_dtype))
+    return fail(B200NORM_ERR_ARG, "unknown dtype code (io %d, w %d)", io_dtype, w_dtype);
+  if (M < 0 || N < 1) return fail(B200NORM_ERR_ARG, "bad shape M=%lld N=%lld", (long long)M, (long long)N);
+  if (N * kernels_for(io_dtype)->elem_size > kMaxRowBytes)
+    return fail(B200NORM_ERR_UNSUPPORTED, "This layer norm doesn't support feature dim >= 64KB.");
+  return B200NORM_OK;
+}
+
+int fwd_impl(int op, const void* x, int64_t xs, const void* w, const void* b, void* y, int64_t ys, float* mean,
+             float* rstd, int64_t M, int64_t N, float eps, int io_dtype, int w_dtype, void* stream) {
+  if (int rc = check_common(M, N, io_dtype, w_dtype)) return rc;
+  if (M == 0) return B200NORM_OK;
+  if (!x || !y || !rstd || (op == kLN && !mean)) return fail(B200NORM_ERR_ARG, "null x / y / mean / rstd");
+  if (xs < N || ys < N) return fail(B200NORM_ERR_ARG, "row stride smaller than N");
+  DeviceState* dev;
+  if (int rc = device_state(&dev)) return rc;
+  const DTypeKernels* k = kernels_for(io_dtype);
+  const int es = k->elem_size;
+
+  FwdParams p;
+  p.x = x; p.y = y; p.w = w; p.b = (op == kLN) ? b : nullptr;
+  p.mean = mean; p.rstd = rstd;
+  p.x_stride = xs; p.y_stride = ys;
+  p.M = M; p.N = static_cast<int>(N); p.V = 0;
+  p.w_dtype = w_dtype; p.eps = eps;
+
+  const bool packets = (N * es) % 16 == 0 && aligned16(x, xs, es) && aligned16(y, ys, es);
+  const PacketKernel* pk = packets ? pick(k->fwd, k->n_fwd, N * es / 16) : nullptr;
+  if (pk != nullptr && pk->packet_params && w_dtype == io_dtype &&
+      (((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(b)) & 15u) != 0))
+    pk = nullptr;
+  if (pk != nullptr) {
+    p.V = static_cast<int>(N * es / 16);
+    int occ;
+    if (int rc = occupancy(*dev, pk->fn[op], pk->threads(), 0, &occ)) return rc;
+    const int64_t want = (M + pk->warps_m - 1) / pk->warps_m;
+    const int grid = static_cast<int>(std::min<int64_t>(want, (int64_t)dev->sm_count * occ));
+    return launch(pk->fn[op], dim3(grid), dim3(pk->threads()), 0, &p, static_cast<cudaStream_t>(stream));
+  }
+  int occ;
+  if (int rc = occupancy(*dev, k->fwd_any[op], 256, 0, &occ)) return rc;
+  const int grid = static_cast<int>(std::min<int64_t>(M, (int64_t)dev->sm_count * occ));
+  return launch(k->fwd_any[op], dim3(grid), dim3(256), 0, &p, static_cast<cudaStream_t>(stream));
+}
+
+// How a backward call is laid out: which kernel, how many partial rows.
+struct BwdPlan {
+  const PacketKernel* pk;  // null: any-alignment kernels
+  int ctas_per_shard;
+  size_t smem;
+};
+
+int any_ctas_per_shard(int64_t rows_per_shard) {
+  return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(256, (rows_per_shard + 63) / 64)));
+}
+
+int plan_bwd(DeviceState& dev, const DTypeKernels* k, int op, int64_t rows_per_shard, int64_t N, bool packets,
+             BwdPlan* plan) {
+  const int es = k->elem_size;
+  plan->pk = packets ? pick(k->bwd, k->n_bwd, N * es / 16) : nullptr;
+  if (plan->pk == nullptr) {
+    plan->ctas_per_shard = any_ctas_per_shard(rows_per_shard);
+    plan->smem = 0;
+    return B200NORM_OK;
+  }
+  const PacketKernel* pk = plan->pk;
+  plan->smem = static_cast<size_t>(pk->warps_m) * N * sizeof(float);
+  int occ;
+  if (int rc = occupancy(dev, pk->fn[op], pk->threads(), plan->smem, &occ)) return rc;
+  const int64_t want = std::max<int64_t>(1, (rows_per_shard + pk->warps_m - 1) / pk->warps_m);
+  plan->ctas_per_shard = static_cast<int>(std::min<int64_t>(want, (int64_t)dev.sm_count * occ));
+  return B200NORM_OK;
+}
+
+size_t partial_bytes(int64_t P, int64_t N) {
+  // one (P, N) fp32 block, rounded so the dbias block that follows stays 256-byte aligned
+  return (static_cast<size_t>(P) * N * sizeof(float) + 255) & ~static_cast<size_t>(255);
+}
+
+int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, const void* w, const float* mean,
+             const float* rstd, void* dx, int64_t dxs, void* dw, void* db, float* group_sums, int row_shards,
+             void* workspace, size_t workspace_bytes, int64_t M, int64_t N, int io_dtype, int w_dtype,
+             void* stream_v) {
+  if (int rc = check_common(M, N, io_dtype, w_dtype)) return rc;
+  if (row_shards < 1 || M % row_shards != 0)
+    return fail(B200NORM_ERR_ARG, "row_shards=%d must be >= 1 and divide M=%lld", row_shards, (long long)M);
+  if (M > 0 && (!x || !dy || !dx || !rstd || (op == kLN && !mean)))
+    return fail(B200NORM_ERR_ARG, "null x / dy / dx / mean / rstd");
+  if (xs < N || dys < N || dxs < N) return fail(B200NORM_ERR_ARG, "row stride smaller than N");
+  if (op == kRMS) db = nullptr;
+  const bool want_params = dw != nullptr || db != nullptr || group_sums != nullptr;
+  if (M == 0 && !want_params) return B200NORM_OK;
+  DeviceState* dev;
+  if (int rc = device_state(&dev)) return rc;
+  const DTypeKernels* k = kernels_for(io_dtype);
+  const int es = k->elem_size;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+  const bool packets =
+      (N * es) % 16 == 0 && aligned16(x, xs, es) && aligned16(dy, dys, es) && aligned16(dx, dxs, es);
+  BwdPlan plan;
+  if (int rc = plan_bwd(*dev, k, op, M / row_shards, N, packets, &plan)) return rc;
+  const int64_t P = (int64_t)plan.ctas_per_shard * row_shards;
+  const int slots = (op == kLN) ? 2 : 1;
+
+  BwdParams p;
+  p.x = x; p.dy = dy; p.w = w; p.mean = mean; p.rstd = rstd; p.dx = dx;
+  p.dw_part = nullptr; p.db_part = nullptr;
+  p.x_stride = xs; p.dy_stride = dys; p.dx_stride = dxs;
+  p.M = M; p.rows_per_shard = M / row_shards; p.ctas_per_shard = plan.ctas_per_shard;
+  p.N = static_cast<int>(N); p.V = static_cast<int>(N * es / 16); p.w_dtype = w_dtype;
+
+  if (want_params) {
+    const size_t need = partial_bytes(P, N) * slots;
+    if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+      return fail(B200NORM_ERR_ARG, "workspace needs %zu bytes, 256-byte aligned (got %zu)", need, workspace_bytes);
+    const bool want_dw = dw != nullptr || group_sums != nullptr;
+    const bool want_db = op == kLN && (db != nullptr || group_sums != nullptr);
+    if (want_dw) p.dw_part = static_cast<float*>(workspace);
+    if (want_db) p.db_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + partial_bytes(P, N));
+  }
+
+  if (plan.pk != nullptr) {
+    if (int rc = launch(plan.pk->fn[op], dim3(static_cast<unsigned>(P)), dim3(plan.pk->threads()), plan.smem, &p,
+                        stream))
+      return rc;
+  } else {
+    if (M > 0) {
+      int occ;
+      if (int rc = occupancy(*dev, k->bwd_dx_any[op], 256, 0, &occ)) return rc;
+      const int grid = static_cast<int>(std::min<int64_t>(M, (int64_t)dev->sm_count * occ));
+      if (int rc = launch(k->bwd_dx_any[op], dim3(grid), dim3(256), 0, &p, stream)) return rc;
+    }
+    if (want_params) {
+      const dim3 grid(static_cast<unsigned>((N + 255) / 256), static_cast<unsigned>(P));
+      if (int rc = launch(k->bwd_dwdb_any[op], grid, dim3(256), 0, &p, stream)) return rc;
+    }
+  }
+  if (!want_params) return B200NORM_OK;
+
+  ColReduceParams c;
+  c.part[0] = p.dw_part; c.part[1] = p.db_part;
+  c.out[0] = dw; c.out[1] = db;
+  c.group_sums = group_sums;
+  c.per_shard = plan.ctas_per_shard; c.row_shards = row_shards; c.slots = slots;
+  c.N = static_cast<int>(N); c.w_dtype = w_dtype;
+  return launch(reinterpret_cast<const void*>(&colreduce_kernel), dim3(static_cast<unsigned>((N + 31) / 32), slots),
+                dim3(32, 16), 0, &c, stream);
+}
+
+}  // namespace
+}  // namespace b200norm
+
+using namespace b200norm;
+
+extern "C" {
+
+int b200norm_version(void) { return B200NORM_VERSION; }
+
+const char* b200norm_last_error(void) { return g_err; }
+
+int b200norm_query(int* sm_count, int* max_partials) {
+  DeviceState* dev;
+  if (int rc = device_state(&dev)) return rc;
+  if (sm_count) *sm_count = dev->sm_count;
+  if (max_partials) *max_partials = std::max(256, dev->sm_count * 16);
+  return B200NORM_OK;
+}
+
+int b200norm_device_status(int clear) {
+  DeviceState* dev;
+  if (device_state(&dev)) return -1;
+  const int v = *static_cast<volatile int*>(dev->status_host);
+  if (clear) *static_cast<volatile int*>(dev->status_host) = 0;
+  return v;
+}
+
+size_t b200norm_bwd_workspace_bytes(int64_t M, int64_t N, int io_dtype, int row_shards) {
+  if (check_common(M, N, io_dtype, B200NORM_F32) || row_shards < 1 || M % row_shards != 0) return 0;
+  DeviceState* dev;
+  if (device_state(&dev)) return 0;
+  const DTypeKernels* k = kernels_for(io_dtype);
+  const int64_t rps = M / row_shards;
+  int64_t per_shard = any_ctas_per_shard(rps);
+  if ((N * k->elem_size) % 16 == 0) {
+    // LayerNorm and RMSNorm instantiations may differ in occupancy: take the larger.
+    for (int op = 0; op < 2; ++op) {
+      BwdPlan plan;
+      if (plan_bwd(*dev, k, op, rps, N, true, &plan)) return 0;
+      per_shard = std::max<int64_t>(per_shard, plan.ctas_per_shard);
+    }
+  }
+  return 2 * partial_bytes(per_shard * row_shards, N);
+}
+
+int b200norm_ln_fwd(const void* x, int64_t x_row_stride, const void* w, const void* b, void* y,
+                    int64_t y_row_stride, float* mean, float* rstd, int64_t M, int64_t N, float eps,
+                    int io_dtype, int w_dtype, void* stream) {
+  return fwd_impl(kLN, x, x_row_stride, w, b, y, y_row_stride, mean, rstd, M, N, eps, io_dtype, w_dtype, stream);
+}
+
+int b200norm_rms_fwd(const void* x, int64_t x_row_stride, const void* w, void* y, int64_t y_row_stride,
+                     float* rstd, int64_t M, int64_t N, float eps, int io_dtype, int w_dtype, void* stream) {
+  return fwd_impl(kRMS, x, x_row_stride, w, nullptr, y, y_row_stride, nullptr, rstd, M, N, eps, io_dtype, w_dtype,
+                  stream);
+}
+
+int b200norm_ln_bwd(const void* x, int64_t x_row_stride, const void* dy, int64_t dy_row_stride,
+                    const void* w, const float* mean, const float* rstd, void* dx, int64_t dx_row_stride,
+                    void* dw, void* db, float* group_sums, int row_shards, void* workspace,
+                    size_t workspace_bytes, int64_t M, int64_t N, int io_dtype, int w_dtype, void* stream) {
+  return bwd_impl(kLN, x, x_row_stride, dy, dy_row_stride, w, mean, rstd, dx, dx_row_stride, dw, db, group_sums,
+                  row_shards, workspace, workspace_bytes, M, N, io_dtype, w_dtype, stream);
+}
+
+int b200norm_rms_bwd(const void* x, int64_t x_row_stride, const void* dy, int64_t dy_row_stride,
+                     const void* w, const float* rstd, void* dx, int64_t dx_row_stride, void* dw,
+                     float* group_sums, int row_shards, void* workspace, size_t workspace_bytes, int64_t M,
+                     int64_t N, int io_dtype, int w_dtype, void* stream) {
+  return bwd_impl(kRMS, x, x_row_stride, dy, dy_row_stride, w, nullptr, rstd, dx, dx_row_stride, dw, nullptr,
+                  group_sums, row_shards, workspace, workspace_bytes, M, N, io_dtype, w_dtype, stream);
+}
+
+int b200norm_finalize_dwdb(const float* group_sums, int groups, int slots, void* dw, void* db, int64_t N,
+                           int w_dtype, void* stream) {
+  if (!group_sums || groups < 1 || (slots != 1 && slots != 2) || N < 1 || !valid_dtype(w_dtype))
+    return fail(B200NORM_ERR_ARG, "bad finalize arguments (groups=%d slots=%d N=%lld)", groups, slots, (long long)N);
+  FinalizeParams p;
+  p.group_sums = group_sums;
+  p.out[0] = dw;
+  p.out[1] = (slots == 2) ? db : nullptr;
+  p.groups = groups; p.slots = slots; p.N = static_cast<int>(N); p.w_dtype = w_dtype;
+  return launch(reinterpret_cast<const void*>(&finalize_kernel), dim3(static_cast<unsigned>((N + 255) / 256), slots),
+                dim3(256), 0, &p, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,217 @@
+// Shared device helpers for the LayerNorm / RMSNorm kernels: 16-byte packets of each storage
+// type, streaming loads and stores, warp and row-group reductions.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200norm {
+
+// Storage type codes; the numbering is the C ABI's enum b200norm_dtype.
+enum : int { kF32 = 0, kF16 = 1, kBF16 = 2, kF64 = 3 };
+
+// ---------------------------------------------------------------------------------------
+// Pack16<T>: one 128-bit packet of T and its fp32 view.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+struct Pack16;
+
+template <>
+struct Pack16<float> {
+  static constexpr int kElems = 4;
+  __device__ __forceinline__ static void unpack(const uint4& v, float* f) {
+    f[0] = __uint_as_float(v.x);
+    f[1] = __uint_as_float(v.y);
+    f[2] = __uint_as_float(v.z);
+    f[3] = __uint_as_float(v.w);
+  }
+  __device__ __forceinline__ static uint4 pack(const float* f) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]),
+                      __float_as_uint(f[3]));
+  }
+};
+
+template <>
+struct Pack16<__half> {
+  static constexpr int kElems = 8;
+  __device__ __forceinline__ static void unpack(const uint4& v, float* f) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+      float2 p = __half22float2(h);
+      f[2 * i] = p.x;
+      f[2 * i + 1] = p.y;
+    }
+  }
+  __device__ __forceinline__ static uint4 pack(const float* f) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+
+template <>
+struct Pack16<__nv_bfloat16> {
+  static constexpr int kElems = 8;
+  __device__ __forceinline__ static void unpack(const uint4& v, float* f) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      // bf16 -> fp32 is a 16-bit shift: exact and cheaper than the library call.
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  __device__ __forceinline__ static uint4 pack(const float* f) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+
+template <>
+struct Pack16<double> {
+  static constexpr int kElems = 2;
+  __device__ __forceinline__ static void unpack(const uint4& v, float* f) {
+    f[0] = static_cast<float>(__hiloint2double(static_cast<int>(v.y), static_cast<int>(v.x)));
+    f[1] = static_cast<float>(__hiloint2double(static_cast<int>(v.w), static_cast<int>(v.z)));
+  }
+  __device__ __forceinline__ static uint4 pack(const float* f) {
+    const double a = static_cast<double>(f[0]), b = static_cast<double>(f[1]);
+    return make_uint4(static_cast<uint32_t>(__double2loint(a)), static_cast<uint32_t>(__double2hiint(a)),
+                      static_cast<uint32_t>(__double2loint(b)), static_cast<uint32_t>(__double2hiint(b)));
+  }
+};
+
+// Scalar conversions for the any-alignment kernels.
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f32(double v) { return static_cast<float>(v); }
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ double from_f32<double>(float v) { return static_cast<double>(v); }
+
+// One element of a parameter vector (weight, bias) whose storage type is only known at run
+// time.  Parameters are read once per CTA, so the switch costs nothing.
+__device__ __forceinline__ float load_param(const void* p, int dtype, int64_t i) {
+  switch (dtype) {
+    case kF32: return static_cast<const float*>(p)[i];
+    case kF16: return __half2float(static_cast<const __half*>(p)[i]);
+    case kBF16: return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+    default: return static_cast<float>(static_cast<const double*>(p)[i]);
+  }
+}
+__device__ __forceinline__ void store_param(void* p, int dtype, int64_t i, float v) {
+  switch (dtype) {
+    case kF32: static_cast<float*>(p)[i] = v; break;
+    case kF16: static_cast<__half*>(p)[i] = __float2half_rn(v); break;
+    case kBF16: static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v); break;
+    default: static_cast<double*>(p)[i] = static_cast<double>(v); break;
+  }
+}
+
+// Storage type code of a compile-time element type.
+template <typename T> struct DTypeOf;
+template <> struct DTypeOf<float> { static constexpr int value = kF32; };
+template <> struct DTypeOf<__half> { static constexpr int value = kF16; };
+template <> struct DTypeOf<__nv_bfloat16> { static constexpr int value = kBF16; };
+template <> struct DTypeOf<double> { static constexpr int value = kF64; };
+
+// The Pack16<T>::kElems parameter values that line up with packet `v` of a row of T: one
+// cached 16-byte load when the parameters are stored as T too, element loads otherwise.
+template <typename T>
+__device__ __forceinline__ void load_param_packet(const void* p, int dtype, int v, float* out) {
+  constexpr int VEC = Pack16<T>::kElems;
+  if (dtype == DTypeOf<T>::value) {
+    const uint4 pk = __ldg(static_cast<const uint4*>(p) + v);
+    Pack16<T>::unpack(pk, out);
+  } else {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) out[e] = load_param(p, dtype, (int64_t)v * VEC + e);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Streaming 128-bit global accesses.  x, dy, y and dx are touched exactly once per kernel, so
+// they bypass L1 on the way in and are marked evict-first on the way out; that keeps L1 for
+// the parameter vectors, which every row re-reads.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_stream(uint4* p, const uint4& v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// ---------------------------------------------------------------------------------------
+// Reductions.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Barrier over the WARPS_N warps that share a row.  Barrier 0 is __syncthreads; row group m
+// uses hardware barrier m+1 (at most 15 row groups per CTA).
+template <int WARPS_N>
+__device__ __forceinline__ void group_sync(int warp_m) {
+  if (WARPS_N > 1) {
+    asm volatile("bar.sync %0, %1;" ::"r"(warp_m + 1), "r"(WARPS_N * 32) : "memory");
+  }
+}
+
+// Sum of NV values over the WARPS_N*32 threads of a row group; every thread gets the result.
+// `scratch` points at this row group's 2*NV*WARPS_N floats of shared memory.  The two halves
+// are used alternately (`phase` flips on every call), so one barrier per call is enough: a
+// warp cannot overwrite a half before every warp has read it, because a full barrier lies
+// between.  The cross-warp add runs in warp order in every thread: deterministic and
+// identical across the group.
+template <int WARPS_N, int NV>
+__device__ __forceinline__ void group_sum(float (&v)[NV], float* scratch, int& phase, int warp_m, int warp_n,
+                                          int lane) {
+#pragma unroll
+  for (int i = 0; i < NV; ++i) v[i] = warp_sum(v[i]);
+  if (WARPS_N > 1) {
+    float* buf = scratch + phase * (NV * WARPS_N);
+    if (lane == 0) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) buf[i * WARPS_N + warp_n] = v[i];
+    }
+    group_sync<WARPS_N>(warp_m);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      float s = 0.f;
+#pragma unroll
+      for (int k = 0; k < WARPS_N; ++k) s += buf[i * WARPS_N + k];
+      v[i] = s;
+    }
+    phase ^= 1;
+  }
+}
+
+}  // namespace b200norm

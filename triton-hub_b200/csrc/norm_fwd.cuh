@@ -1,0 +1,167 @@
+// Forward kernels: LayerNorm (TritonHub/Normalization/layernorm.py:14-46) and RMSNorm
+// (TritonHub/Normalization/rmsnorm.py:14-38) with the whole row held in registers.
+#pragma once
+
+#include "norm_common.cuh"
+
+namespace b200norm {
+
+struct FwdParams {
+  const void* x;
+  void* y;
+  const void* w;  // may be null
+  const void* b;  // may be null (always null for RMSNorm)
+  float* mean;    // (M,) LayerNorm only
+  float* rstd;    // (M,)
+  int64_t x_stride;  // elements
+  int64_t y_stride;
+  int64_t M;
+  int N;        // elements per row
+  int V;        // 16-byte packets per row (packet kernels only)
+  int w_dtype;  // storage type of w and b
+  float eps;
+};
+
+// Packet kernel.  A CTA is WARPS_M row groups of WARPS_N warps; a row group owns one row at a
+// time and walks the rows grid-strided.  Thread t of the group holds packets t, t+TPR, ... of
+// the row (LDGS of them, predicated on the row length), so every warp-wide access is one
+// contiguous 512-byte segment.  With PREG, weight and bias sit in fp32 registers for the life
+// of the CTA; without it (rows too wide to spare the registers) each row re-reads them through
+// L1, which needs 16-byte aligned parameter vectors when they are stored as T.
+//
+// Statistics follow the reference exactly: mean, then the centred sum of squares over the
+// registers (layernorm.py:32-35), never E[x^2]-E[x]^2.
+template <typename T, int LDGS, int WARPS_M, int WARPS_N, bool PREG, bool RMS>
+__global__ void __launch_bounds__(WARPS_M* WARPS_N * 32) norm_fwd_kernel(const FwdParams p) {
+  constexpr int VEC = Pack16<T>::kElems;
+  constexpr int TPR = WARPS_N * 32;  // threads per row
+  __shared__ float red_smem[WARPS_M][2 * WARPS_N];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp_m = warp / WARPS_N, warp_n = warp % WARPS_N;
+  const int t = warp_n * 32 + lane;
+  int phase = 0;
+
+  constexpr int PL = PREG ? LDGS : 1;
+  float wr[PL][VEC], br[PL][VEC];
+#pragma unroll
+  for (int j = 0; j < PL; ++j) {
+    const int v = j * TPR + t;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      wr[j][e] = 1.f;
+      br[j][e] = 0.f;
+    }
+    if (PREG && v < p.V) {
+      if (p.w != nullptr) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) wr[j][e] = load_param(p.w, p.w_dtype, (int64_t)v * VEC + e);
+      }
+      if (!RMS && p.b != nullptr) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) br[j][e] = load_param(p.b, p.w_dtype, (int64_t)v * VEC + e);
+      }
+    }
+  }
+
+  const float inv_n = 1.f / static_cast<float>(p.N);
+  const T* xb = static_cast<const T*>(p.x);
+  T* yb = static_cast<T*>(p.y);
+
+  for (int64_t row = (int64_t)blockIdx.x * WARPS_M + warp_m; row < p.M; row += (int64_t)gridDim.x * WARPS_M) {
+    const uint4* xrow = reinterpret_cast<const uint4*>(xb + row * p.x_stride);
+    float xf[LDGS][VEC];
+#pragma unroll
+    for (int j = 0; j < LDGS; ++j) {
+      const int v = j * TPR + t;
+      uint4 pk = make_uint4(0, 0, 0, 0);
+      if (v < p.V) pk = ld_stream(xrow + v);
+      Pack16<T>::unpack(pk, xf[j]);
+    }
+
+    float mean = 0.f;
+    if (!RMS) {
+      float s[1] = {0.f};
+#pragma unroll
+      for (int j = 0; j < LDGS; ++j)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) s[0] += xf[j][e];
+      group_sum<WARPS_N, 1>(s, red_smem[warp_m], phase, warp_m, warp_n, lane);
+      mean = s[0] * inv_n;
+    }
+    float q[1] = {0.f};
+#pragma unroll
+    for (int j = 0; j < LDGS; ++j) {
+      const bool live = (j * TPR + t) < p.V;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        const float d = live ? (xf[j][e] - mean) : 0.f;
+        q[0] += d * d;
+      }
+    }
+    group_sum<WARPS_N, 1>(q, red_smem[warp_m], phase, warp_m, warp_n, lane);
+    const float rstd = 1.f / sqrtf(q[0] * inv_n + p.eps);
+    if (t == 0) {
+      if (!RMS) p.mean[row] = mean;
+      p.rstd[row] = rstd;
+    }
+
+    uint4* yrow = reinterpret_cast<uint4*>(yb + row * p.y_stride);
+#pragma unroll
+    for (int j = 0; j < LDGS; ++j) {
+      const int v = j * TPR + t;
+      float yf[VEC];
+      if (PREG) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) yf[e] = (xf[j][e] - mean) * rstd * wr[j][e] + br[j][e];
+      } else if (v < p.V) {
+        if (p.w != nullptr) load_param_packet<T>(p.w, p.w_dtype, v, wr[0]);
+        if (!RMS && p.b != nullptr) load_param_packet<T>(p.b, p.w_dtype, v, br[0]);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) yf[e] = (xf[j][e] - mean) * rstd * wr[0][e] + br[0][e];
+      }
+      if (v < p.V) st_stream(yrow + v, Pack16<T>::pack(yf));
+    }
+  }
+}
+
+// Any-alignment kernel: one CTA per row, scalar accesses, three passes over the row (the
+// second and third hit L1/L2).  Serves rows whose length, base address or stride is not a
+// multiple of 16 bytes.
+template <typename T, bool RMS>
+__global__ void __launch_bounds__(256) norm_fwd_any_kernel(const FwdParams p) {
+  __shared__ float red[2][8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int phase = 0;
+  const float inv_n = 1.f / static_cast<float>(p.N);
+  for (int64_t row = blockIdx.x; row < p.M; row += gridDim.x) {
+    const T* xrow = static_cast<const T*>(p.x) + row * p.x_stride;
+    T* yrow = static_cast<T*>(p.y) + row * p.y_stride;
+    float mean = 0.f;
+    if (!RMS) {
+      float s[1] = {0.f};
+      for (int c = threadIdx.x; c < p.N; c += 256) s[0] += to_f32(xrow[c]);
+      group_sum<8, 1>(s, &red[0][0], phase, -1, warp, lane);
+      mean = s[0] * inv_n;
+    }
+    float q[1] = {0.f};
+    for (int c = threadIdx.x; c < p.N; c += 256) {
+      const float d = to_f32(xrow[c]) - mean;
+      q[0] += d * d;
+    }
+    group_sum<8, 1>(q, &red[0][0], phase, -1, warp, lane);
+    const float rstd = 1.f / sqrtf(q[0] * inv_n + p.eps);
+    if (threadIdx.x == 0) {
+      if (!RMS) p.mean[row] = mean;
+      p.rstd[row] = rstd;
+    }
+    for (int c = threadIdx.x; c < p.N; c += 256) {
+      float yv = (to_f32(xrow[c]) - mean) * rstd;
+      if (p.w != nullptr) yv *= load_param(p.w, p.w_dtype, c);
+      if (!RMS && p.b != nullptr) yv += load_param(p.b, p.w_dtype, c);
+      yrow[c] = from_f32<T>(yv);
+    }
+  }
+}
+
+}  // namespace b200norm

@@ -1,0 +1,34 @@
+// Host-side description of the compiled kernels: one table per storage type, filled in by
+// the per-type translation units and consulted by the launch code.  This fixed table is
+// what stands in for the reference's run-time autotuner (TritonHub/autotune.py:61-65).
+#pragma once
+
+namespace b200norm {
+
+// A packet kernel instantiation: each thread holds `ldgs` 16-byte packets of the row, a row
+// is spread over `warps_n` warps, and a CTA runs `warps_m` such row groups side by side.
+struct PacketKernel {
+  int ldgs, warps_m, warps_n;
+  bool packet_params;  // re-reads weight / bias per row as 16-byte packets: they must be aligned
+  const void* fn[2];   // [0] LayerNorm, [1] RMSNorm
+  int capacity() const { return ldgs * 32 * warps_n; }  // packets per row it can hold
+  int threads() const { return 32 * warps_m * warps_n; }
+};
+
+struct DTypeKernels {
+  int elem_size;
+  const PacketKernel* fwd;  // ascending capacity
+  int n_fwd;
+  const PacketKernel* bwd;  // ascending capacity
+  int n_bwd;
+  const void* fwd_any[2];
+  const void* bwd_dx_any[2];
+  const void* bwd_dwdb_any[2];
+};
+
+const DTypeKernels* kernels_f32();
+const DTypeKernels* kernels_f16();
+const DTypeKernels* kernels_bf16();
+const DTypeKernels* kernels_f64();
+
+}  // namespace b200norm
