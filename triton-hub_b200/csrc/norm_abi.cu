@@ -76,7 +76,7 @@ int occupancy(DeviceState& s, const void* fn, int threads, size_t smem, int* out
     return B200NORM_OK;
   }
   cudaError_t e;
-  if (smem > 48 * 1024) {
+  if (smem > 32 * 1024) {  // static shared memory counts toward the 48 KB default limit too
     e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess)
       return fail(B200NORM_ERR_CUDA, "cudaFuncSetAttribute(%zu B): %s", smem, cudaGetErrorString(e));
@@ -145,20 +145,21 @@ int fwd_impl(int op, const void* x, int64_t xs, const void* w, const void* b, vo
   p.mean = mean; p.rstd = rstd;
   p.x_stride = xs; p.y_stride = ys;
   p.M = M; p.N = static_cast<int>(N); p.V = 0;
-  p.w_dtype = w_dtype; p.eps = eps;
+  p.w_dtype = w_dtype; p.eps = eps; p.status = dev->status_dev;
 
   const bool packets = (N * es) % 16 == 0 && aligned16(x, xs, es) && aligned16(y, ys, es);
-  const PacketKernel* pk = packets ? pick(k->fwd, k->n_fwd, N * es / 16) : nullptr;
+  const PacketKernel* pk = packets ? pick(k->fwd[op], k->n_fwd[op], N * es / 16) : nullptr;
   if (pk != nullptr && pk->packet_params && w_dtype == io_dtype &&
       (((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(b)) & 15u) != 0))
     pk = nullptr;
   if (pk != nullptr) {
     p.V = static_cast<int>(N * es / 16);
+    const size_t smem = static_cast<size_t>(pk->warps_m) * pk->stages * p.V * 16;  // the row slots
     int occ;
-    if (int rc = occupancy(*dev, pk->fn[op], pk->threads(), 0, &occ)) return rc;
+    if (int rc = occupancy(*dev, pk->fn, pk->threads(), smem, &occ)) return rc;
     const int64_t want = (M + pk->warps_m - 1) / pk->warps_m;
     const int grid = static_cast<int>(std::min<int64_t>(want, (int64_t)dev->sm_count * occ));
-    return launch(pk->fn[op], dim3(grid), dim3(pk->threads()), 0, &p, static_cast<cudaStream_t>(stream));
+    return launch(pk->fn, dim3(grid), dim3(pk->threads()), smem, &p, static_cast<cudaStream_t>(stream));
   }
   int occ;
   if (int rc = occupancy(*dev, k->fwd_any[op], 256, 0, &occ)) return rc;
@@ -180,16 +181,18 @@ int any_ctas_per_shard(int64_t rows_per_shard) {
 int plan_bwd(DeviceState& dev, const DTypeKernels* k, int op, int64_t rows_per_shard, int64_t N, bool packets,
              BwdPlan* plan) {
   const int es = k->elem_size;
-  plan->pk = packets ? pick(k->bwd, k->n_bwd, N * es / 16) : nullptr;
+  plan->pk = packets ? pick(k->bwd[op], k->n_bwd[op], N * es / 16) : nullptr;
   if (plan->pk == nullptr) {
     plan->ctas_per_shard = any_ctas_per_shard(rows_per_shard);
     plan->smem = 0;
     return B200NORM_OK;
   }
   const PacketKernel* pk = plan->pk;
-  plan->smem = static_cast<size_t>(pk->warps_m) * N * sizeof(float);
+  // fp32 weights / cross-group sums, padded to 128 bytes, then the x+dy row slots
+  plan->smem = ((static_cast<size_t>(pk->warps_m) * N * sizeof(float) + 127) & ~static_cast<size_t>(127)) +
+               static_cast<size_t>(pk->warps_m) * pk->stages * 2 * (N * es);
   int occ;
-  if (int rc = occupancy(dev, pk->fn[op], pk->threads(), plan->smem, &occ)) return rc;
+  if (int rc = occupancy(dev, pk->fn, pk->threads(), plan->smem, &occ)) return rc;
   const int64_t want = std::max<int64_t>(1, (rows_per_shard + pk->warps_m - 1) / pk->warps_m);
   plan->ctas_per_shard = static_cast<int>(std::min<int64_t>(want, (int64_t)dev.sm_count * occ));
   return B200NORM_OK;
@@ -232,6 +235,7 @@ int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, con
   p.x_stride = xs; p.dy_stride = dys; p.dx_stride = dxs;
   p.M = M; p.rows_per_shard = M / row_shards; p.ctas_per_shard = plan.ctas_per_shard;
   p.N = static_cast<int>(N); p.V = static_cast<int>(N * es / 16); p.w_dtype = w_dtype;
+  p.status = dev->status_dev;
 
   if (want_params) {
     const size_t need = partial_bytes(P, N) * slots;
@@ -244,7 +248,7 @@ int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, con
   }
 
   if (plan.pk != nullptr) {
-    if (int rc = launch(plan.pk->fn[op], dim3(static_cast<unsigned>(P)), dim3(plan.pk->threads()), plan.smem, &p,
+    if (int rc = launch(plan.pk->fn, dim3(static_cast<unsigned>(P)), dim3(plan.pk->threads()), plan.smem, &p,
                         stream))
       return rc;
   } else {

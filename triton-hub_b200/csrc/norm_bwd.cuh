@@ -4,6 +4,7 @@
 #pragma once
 
 #include "norm_common.cuh"
+#include "norm_stage.cuh"
 
 namespace b200norm {
 
@@ -25,49 +26,89 @@ struct BwdParams {
   int N;
   int V;  // 16-byte packets per row (packet kernels only)
   int w_dtype;
+  int* status;  // device status word for bounded waits that ran out
 };
 
 // Packet kernel.  Same thread-to-column map as the forward kernel, so each thread owns a
 // fixed set of columns and carries their dweight / dbias sums in fp32 registers across all
 // the rows its row group visits.  x and dy stay packed in registers; xhat and w*dy are
 // recomputed for the dx pass instead of being kept, which is what lets a 32 KB row fit.
-// With PREFETCH the next row's packets are requested before the current row is reduced, so
-// each row group always has loads in flight; the widest rows cannot spare those registers.
 // The weight vector lives in shared memory as fp32.
+//
+// How rows arrive:
+//   STAGES > 0   x and dy rows are staged through a ring of STAGES shared-memory slots per row
+//                group by bulk asynchronous copies (norm_stage.cuh); the leader refills a slot
+//                right after the row's reduction, which every thread passes only once its
+//                shared-memory reads have returned.
+//   PREFETCH     (STAGES == 0) the next row's packets are requested into registers before the
+//                current row is reduced.
+//   neither      plain streaming loads, one row at a time.
 //
 // Row shards: CTA c serves shard c / ctas_per_shard and walks that shard's rows strided by
 // ctas_per_shard * WARPS_M.  The rows a CTA sums, and their order, depend only on the shard's
 // size -- not on how many shards this launch covers -- so one launch over 8 shards and 8
 // launches (8 GPUs) over one shard each produce the same partial rows bit for bit.
-template <typename T, int LDGS, int WARPS_M, int WARPS_N, bool PREFETCH, bool RMS>
-__global__ void __launch_bounds__(WARPS_M* WARPS_N * 32) norm_bwd_kernel(const BwdParams p) {
+//
+// KEEP: xhat and w*dy of the current row stay in fp32 registers between the two passes
+// instead of being recomputed from the packed row (fewer instructions, more registers).
+// MINB is the number of CTAs per SM the register allocation must leave room for.
+template <typename T, int LDGS, int WARPS_M, int WARPS_N, bool PREFETCH, int STAGES, bool KEEP, int MINB, bool RMS>
+__global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(const BwdParams p) {
   constexpr int VEC = Pack16<T>::kElems;
   constexpr int TPR = WARPS_N * 32;
   constexpr int NV = RMS ? 1 : 2;
-  extern __shared__ __align__(16) float dyn_smem[];  // w as fp32 (N), later (WARPS_M, N) sums
+  constexpr int NBAR = STAGES > 0 ? WARPS_M * STAGES : 1;
+  // w as fp32 (N), later the (WARPS_M, N) sums; then, 128-byte aligned, the row slots
+  extern __shared__ __align__(128) unsigned char dyn_smem[];
   __shared__ float red_smem[WARPS_M][2 * NV * WARPS_N];
+  __shared__ __align__(8) uint64_t full_bar[NBAR];
+  __shared__ int cta_abort;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warp_m = warp / WARPS_N, warp_n = warp % WARPS_N;
   const int t = warp_n * 32 + lane;
   int phase = 0;
 
-  float* w_s = dyn_smem;
-  for (int c = threadIdx.x; c < p.N; c += WARPS_M * TPR)
-    w_s[c] = (p.w != nullptr) ? load_param(p.w, p.w_dtype, c) : 1.f;
-  __syncthreads();
-
   const int shard = blockIdx.x / p.ctas_per_shard;
   const int cta_in_shard = blockIdx.x - shard * p.ctas_per_shard;
   const int64_t row_begin = (int64_t)shard * p.rows_per_shard;
   const int64_t row_end = min(row_begin + p.rows_per_shard, p.M);
   const int64_t step = (int64_t)p.ctas_per_shard * WARPS_M;
-  int64_t row = row_begin + (int64_t)cta_in_shard * WARPS_M + warp_m;
+  const int64_t first = row_begin + (int64_t)cta_in_shard * WARPS_M + warp_m;
 
   const T* xb = static_cast<const T*>(p.x);
   const T* gb = static_cast<const T*>(p.dy);
   T* dxb = static_cast<T*>(p.dx);
   const float inv_n = 1.f / static_cast<float>(p.N);
+
+  float* w_s = reinterpret_cast<float*>(dyn_smem);
+  const uint32_t row_bytes = static_cast<uint32_t>(p.V) * 16u;
+  const size_t param_bytes = ((size_t)WARPS_M * p.N * sizeof(float) + 127) & ~(size_t)127;
+  unsigned char* slots = dyn_smem + param_bytes + (size_t)warp_m * STAGES * 2 * row_bytes;
+  uint64_t* bars = full_bar + (STAGES > 0 ? warp_m * STAGES : 0);
+
+  auto fill = [&](int s, int64_t r) {  // leader only: x row then dy row into slot s
+    unsigned char* dst = slots + (size_t)s * 2 * row_bytes;
+    mbar_expect_tx(&bars[s], 2 * row_bytes);
+    bulk_load(dst, xb + r * p.x_stride, row_bytes, &bars[s]);
+    bulk_load(dst + row_bytes, gb + r * p.dy_stride, row_bytes, &bars[s]);
+  };
+
+  if (STAGES > 0 && threadIdx.x == 0) {
+    for (int i = 0; i < NBAR; ++i) mbar_init(&full_bar[i], 1);
+    cta_abort = 0;
+    mbar_init_fence();
+  }
+  for (int c = threadIdx.x; c < p.N; c += WARPS_M * TPR)
+    w_s[c] = (p.w != nullptr) ? load_param(p.w, p.w_dtype, c) : 1.f;
+  __syncthreads();
+  if (STAGES > 0 && t == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      const int64_t r = first + s * step;
+      if (r < row_end) fill(s, r);
+    }
+  }
 
   float dw[LDGS][VEC], db[LDGS][VEC];
 #pragma unroll
@@ -76,8 +117,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32) norm_bwd_kernel(const B
     for (int e = 0; e < VEC; ++e) dw[j][e] = db[j][e] = 0.f;
 
   uint4 xv[LDGS], gv[LDGS];
-  float mu = 0.f, rs = 0.f;
-  auto fetch = [&](int64_t r, uint4* xo, uint4* go, float& m_o, float& r_o) {
+  auto fetch = [&](int64_t r, uint4* xo, uint4* go) {  // STAGES == 0: straight from global
     const uint4* xrow = reinterpret_cast<const uint4*>(xb + r * p.x_stride);
     const uint4* grow = reinterpret_cast<const uint4*>(gb + r * p.dy_stride);
 #pragma unroll
@@ -90,24 +130,50 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32) norm_bwd_kernel(const B
         go[j] = ld_stream(grow + v);
       }
     }
-    m_o = RMS ? 0.f : __ldg(p.mean + r);
-    r_o = __ldg(p.rstd + r);
   };
 
-  if (row < row_end) fetch(row, xv, gv, mu, rs);
+  int64_t row = first;
+  float mu = 0.f, rs = 0.f;
+  if (row < row_end) {
+    if (STAGES == 0) fetch(row, xv, gv);
+    mu = RMS ? 0.f : __ldg(p.mean + row);
+    rs = __ldg(p.rstd + row);
+  }
+  int slot = 0;
+  uint32_t parity = 0;
+
   while (row < row_end) {
     const int64_t next = row + step;
-    constexpr int NL = PREFETCH ? LDGS : 1;
+    constexpr int NL = (PREFETCH && STAGES == 0) ? LDGS : 1;
     uint4 xn[NL], gn[NL];
     float mun = 0.f, rsn = 0.f;
-    if (PREFETCH) {
-      if (next < row_end) fetch(next, xn, gn, mun, rsn);
+    if (next < row_end) {  // the next row's statistics are always requested one row ahead
+      mun = RMS ? 0.f : __ldg(p.mean + next);
+      rsn = __ldg(p.rstd + next);
+      if (PREFETCH && STAGES == 0) fetch(next, xn, gn);
+    }
+    if (STAGES > 0) {
+      mbar_wait(&bars[slot], parity, &cta_abort, p.status);
+      const uint4* sx = reinterpret_cast<const uint4*>(slots + (size_t)slot * 2 * row_bytes);
+      const uint4* sg = reinterpret_cast<const uint4*>(slots + (size_t)slot * 2 * row_bytes + row_bytes);
+#pragma unroll
+      for (int j = 0; j < LDGS; ++j) {
+        const int v = j * TPR + t;
+        xv[j] = make_uint4(0, 0, 0, 0);
+        gv[j] = make_uint4(0, 0, 0, 0);
+        if (v < p.V) {
+          xv[j] = ld_shared16(sx + v);
+          gv[j] = ld_shared16(sg + v);
+        }
+      }
     }
 
     // Pass 1: dweight / dbias sums and the two row sums (layernorm.py:132-138).
     float s[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) s[i] = 0.f;
+    constexpr int KL = KEEP ? LDGS : 1;
+    float xh_k[KL][VEC], wdy_k[KL][VEC];
 #pragma unroll
     for (int j = 0; j < LDGS; ++j) {
       const int v = j * TPR + t;
@@ -123,10 +189,25 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32) norm_bwd_kernel(const B
           if (!RMS) db[j][e] += gf[e];
           s[0] += xh * wdy;
           if (!RMS) s[NV - 1] += wdy;
+          if (KEEP) {
+            xh_k[j][e] = xh;
+            wdy_k[j][e] = wdy;
+          }
         }
       }
     }
     group_sum<WARPS_N, NV>(s, red_smem[warp_m], phase, warp_m, warp_n, lane);
+    if (STAGES > 0) {
+      // Every thread of the group holds its packets in registers: the slot can be refilled.
+      if (t == 0) {
+        const int64_t r = row + STAGES * step;
+        if (r < row_end) fill(slot, r);
+      }
+      if (++slot == STAGES) {
+        slot = 0;
+        parity ^= 1u;
+      }
+    }
     const float c1 = s[0] * inv_n;
     const float c2 = RMS ? 0.f : s[NV - 1] * inv_n;
 
@@ -136,36 +217,47 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32) norm_bwd_kernel(const B
     for (int j = 0; j < LDGS; ++j) {
       const int v = j * TPR + t;
       if (v < p.V) {
-        float xf[VEC], gf[VEC], o[VEC];
-        Pack16<T>::unpack(xv[j], xf);
-        Pack16<T>::unpack(gv[j], gf);
+        float o[VEC];
+        if (KEEP) {
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-          const float xh = (xf[e] - mu) * rs;
-          const float wdy = w_s[v * VEC + e] * gf[e];
-          o[e] = (wdy - (xh * c1 + c2)) * rs;
+          for (int e = 0; e < VEC; ++e) o[e] = (wdy_k[j][e] - (xh_k[j][e] * c1 + c2)) * rs;
+        } else {
+          float xf[VEC], gf[VEC];
+          Pack16<T>::unpack(xv[j], xf);
+          Pack16<T>::unpack(gv[j], gf);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) {
+            const float xh = (xf[e] - mu) * rs;
+            const float wdy = w_s[v * VEC + e] * gf[e];
+            o[e] = (wdy - (xh * c1 + c2)) * rs;
+          }
         }
         st_stream(dxrow + v, Pack16<T>::pack(o));
       }
     }
 
     row = next;
-    if (PREFETCH) {
+    mu = mun;
+    rs = rsn;
+    if (STAGES == 0) {
+      if (PREFETCH) {
 #pragma unroll
-      for (int j = 0; j < NL; ++j) {
-        xv[j] = xn[j];
-        gv[j] = gn[j];
+        for (int j = 0; j < NL; ++j) {
+          xv[j] = xn[j];
+          gv[j] = gn[j];
+        }
+      } else if (row < row_end) {
+        fetch(row, xv, gv);
       }
-      mu = mun;
-      rs = rsn;
-    } else if (row < row_end) {
-      fetch(row, xv, gv, mu, rs);
     }
+  }
+  if (STAGES > 0) {
+    if (t == 0 && cta_abort) drain_ring<STAGES>(bars, first < row_end ? (row_end - first + step - 1) / step : 0);
   }
 
   // One partial row per CTA: add the row groups in order, then row group 0 stores.
   if (WARPS_M > 1) {
-    float* acc = dyn_smem;  // (WARPS_M, N); the weights are no longer needed
+    float* acc = reinterpret_cast<float*>(dyn_smem);  // (WARPS_M, N); the weights are no longer needed
 #pragma unroll
     for (int pass = 0; pass < NV; ++pass) {
       __syncthreads();

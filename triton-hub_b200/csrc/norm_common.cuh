@@ -214,4 +214,49 @@ __device__ __forceinline__ void group_sum(float (&v)[NV], float* scratch, int& p
   }
 }
 
+// Mean and centred sum of squares of a row from per-thread (mean, M2) pairs over equal element
+// counts, merged pairwise with Chan's update
+//   n = na + nb;  d = mb - ma;  mean = ma + d * nb / n;  M2 = M2a + M2b + d * d * na * nb / n
+// -- one reduction (one barrier) per row where the two-pass form needs two, with the same
+// numerical quality: no E[x^2] - E[x]^2 cancellation.  With equal counts the weights are
+// constants (nb/n = 1/2 in the butterfly, 1/(k+1) across warps), so nothing is divided and both
+// butterfly partners compute the same bits.  The warp pairs go through shared memory and every
+// thread folds them in warp order: the whole row group ends with identical statistics.
+// `n` is the element count per thread on entry and per row group on return.
+template <int WARPS_N>
+__device__ __forceinline__ void group_moments(float& n, float& mean, float& m2, float* scratch, int& phase,
+                                              int warp_m, int warp_n, int lane) {
+  float half = 0.5f * n;  // na * nb / (na + nb) for equal counts
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float mb = __shfl_xor_sync(0xffffffffu, mean, o);
+    const float qb = __shfl_xor_sync(0xffffffffu, m2, o);
+    const float d = mb - mean;
+    mean = 0.5f * (mean + mb);
+    m2 = (m2 + qb) + d * d * half;
+    half += half;
+  }
+  n *= 32.f;
+  if (WARPS_N > 1) {
+    float* buf = scratch + phase * (2 * WARPS_N);
+    if (lane == 0) {
+      buf[warp_n] = mean;
+      buf[WARPS_N + warp_n] = m2;
+    }
+    group_sync<WARPS_N>(warp_m);
+    const float nw = n;  // elements per warp
+    mean = buf[0];
+    m2 = buf[WARPS_N];
+#pragma unroll
+    for (int k = 1; k < WARPS_N; ++k) {
+      const float f = 1.f / static_cast<float>(k + 1);  // folded at compile time
+      const float d = buf[k] - mean;
+      mean = mean + d * f;
+      m2 = (m2 + buf[WARPS_N + k]) + d * d * (static_cast<float>(k) * f * nw);
+    }
+    n = nw * static_cast<float>(WARPS_N);
+    phase ^= 1;
+  }
+}
+
 }  // namespace b200norm

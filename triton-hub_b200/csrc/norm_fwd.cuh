@@ -3,6 +3,7 @@
 #pragma once
 
 #include "norm_common.cuh"
+#include "norm_stage.cuh"
 
 namespace b200norm {
 
@@ -20,27 +21,71 @@ struct FwdParams {
   int V;        // 16-byte packets per row (packet kernels only)
   int w_dtype;  // storage type of w and b
   float eps;
+  int* status;  // device status word for bounded waits that ran out
 };
 
 // Packet kernel.  A CTA is WARPS_M row groups of WARPS_N warps; a row group owns one row at a
 // time and walks the rows grid-strided.  Thread t of the group holds packets t, t+TPR, ... of
 // the row (LDGS of them, predicated on the row length), so every warp-wide access is one
-// contiguous 512-byte segment.  With PREG, weight and bias sit in fp32 registers for the life
-// of the CTA; without it (rows too wide to spare the registers) each row re-reads them through
-// L1, which needs 16-byte aligned parameter vectors when they are stored as T.
+// contiguous 512-byte segment.
 //
-// Statistics follow the reference exactly: mean, then the centred sum of squares over the
-// registers (layernorm.py:32-35), never E[x^2]-E[x]^2.
-template <typename T, int LDGS, int WARPS_M, int WARPS_N, bool PREG, bool RMS>
-__global__ void __launch_bounds__(WARPS_M* WARPS_N * 32) norm_fwd_kernel(const FwdParams p) {
+// PREG: weight and bias sit in fp32 registers for the life of the CTA; without it each row
+// re-reads them through L1 as packets (needs 16-byte aligned parameter vectors when they are
+// stored as T), which frees registers for occupancy.
+//
+// STAGES > 0: rows reach the registers through a ring of STAGES shared-memory slots per row
+// group, filled by bulk asynchronous copies (norm_stage.cuh).  The group's leader refills a
+// slot right after the row's first reduction, which every thread passes only once its
+// shared-memory reads have returned.  STAGES == 0: plain streaming loads from global memory.
+//
+// Statistics: when every thread of a row group holds the same number of elements, each thread
+// forms the mean and the centred sum of squares of its own elements (two passes over registers,
+// as layernorm.py:32-35 does for the whole row) and the group merges them with Chan's update
+// (norm_common.cuh) in ONE reduction; ragged rows take the reference's two reductions.  Never
+// E[x^2]-E[x]^2.
+//
+// MINB is the number of CTAs per SM the register allocation must leave room for.
+template <typename T, int LDGS, int WARPS_M, int WARPS_N, bool PREG, int STAGES, int MINB, bool RMS>
+__global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(const FwdParams p) {
   constexpr int VEC = Pack16<T>::kElems;
   constexpr int TPR = WARPS_N * 32;  // threads per row
-  __shared__ float red_smem[WARPS_M][2 * WARPS_N];
+  constexpr int NBAR = STAGES > 0 ? WARPS_M * STAGES : 1;
+  extern __shared__ __align__(128) unsigned char dyn_smem[];  // (WARPS_M, STAGES, row bytes)
+  __shared__ float red_smem[WARPS_M][2 * 3 * WARPS_N];
+  __shared__ __align__(8) uint64_t full_bar[NBAR];
+  __shared__ int cta_abort;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warp_m = warp / WARPS_N, warp_n = warp % WARPS_N;
   const int t = warp_n * 32 + lane;
   int phase = 0;
+
+  const T* xb = static_cast<const T*>(p.x);
+  T* yb = static_cast<T*>(p.y);
+  const int64_t first = (int64_t)blockIdx.x * WARPS_M + warp_m;
+  const int64_t step = (int64_t)gridDim.x * WARPS_M;
+  const uint32_t row_bytes = static_cast<uint32_t>(p.V) * 16u;
+  unsigned char* slots = dyn_smem + (size_t)warp_m * STAGES * row_bytes;
+  uint64_t* bars = full_bar + (STAGES > 0 ? warp_m * STAGES : 0);
+
+  if (STAGES > 0) {
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < NBAR; ++i) mbar_init(&full_bar[i], 1);
+      cta_abort = 0;
+      mbar_init_fence();
+    }
+    __syncthreads();
+    if (t == 0) {
+#pragma unroll
+      for (int s = 0; s < STAGES; ++s) {
+        const int64_t r = first + s * step;
+        if (r < p.M) {
+          mbar_expect_tx(&bars[s], row_bytes);
+          bulk_load(slots + (size_t)s * row_bytes, xb + r * p.x_stride, row_bytes, &bars[s]);
+        }
+      }
+    }
+  }
 
   constexpr int PL = PREG ? LDGS : 1;
   float wr[PL][VEC], br[PL][VEC];
@@ -65,41 +110,97 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32) norm_fwd_kernel(const F
   }
 
   const float inv_n = 1.f / static_cast<float>(p.N);
-  const T* xb = static_cast<const T*>(p.x);
-  T* yb = static_cast<T*>(p.y);
+  const bool uniform = (p.V % TPR) == 0 && p.V >= TPR;  // every thread of a row group holds the same element count
+  // uniform rows: each thread holds V / TPR packets
+  const float thread_cnt = static_cast<float>((p.V / TPR) * VEC);
+  const float thread_inv_cnt = 1.f / (thread_cnt > 0.f ? thread_cnt : 1.f);
+  int slot = 0;
+  uint32_t parity = 0;
 
-  for (int64_t row = (int64_t)blockIdx.x * WARPS_M + warp_m; row < p.M; row += (int64_t)gridDim.x * WARPS_M) {
-    const uint4* xrow = reinterpret_cast<const uint4*>(xb + row * p.x_stride);
+  for (int64_t row = first; row < p.M; row += step) {
     float xf[LDGS][VEC];
+    if (STAGES > 0) {
+      mbar_wait(&bars[slot], parity, &cta_abort, p.status);
+      const uint4* srow = reinterpret_cast<const uint4*>(slots + (size_t)slot * row_bytes);
 #pragma unroll
-    for (int j = 0; j < LDGS; ++j) {
-      const int v = j * TPR + t;
-      uint4 pk = make_uint4(0, 0, 0, 0);
-      if (v < p.V) pk = ld_stream(xrow + v);
-      Pack16<T>::unpack(pk, xf[j]);
+      for (int j = 0; j < LDGS; ++j) {
+        const int v = j * TPR + t;
+        uint4 pk = make_uint4(0, 0, 0, 0);
+        if (v < p.V) pk = ld_shared16(srow + v);
+        Pack16<T>::unpack(pk, xf[j]);
+      }
+    } else {
+      const uint4* xrow = reinterpret_cast<const uint4*>(xb + row * p.x_stride);
+#pragma unroll
+      for (int j = 0; j < LDGS; ++j) {
+        const int v = j * TPR + t;
+        uint4 pk = make_uint4(0, 0, 0, 0);
+        if (v < p.V) pk = ld_stream(xrow + v);
+        Pack16<T>::unpack(pk, xf[j]);
+      }
     }
 
     float mean = 0.f;
+    float q[1] = {0.f};
     if (!RMS) {
       float s[1] = {0.f};
 #pragma unroll
       for (int j = 0; j < LDGS; ++j)
 #pragma unroll
         for (int e = 0; e < VEC; ++e) s[0] += xf[j][e];
-      group_sum<WARPS_N, 1>(s, red_smem[warp_m], phase, warp_m, warp_n, lane);
-      mean = s[0] * inv_n;
+      if (uniform) {
+        // One reduction: per-thread mean and centred squares, merged with Chan's update.
+        float cnt = thread_cnt;
+        mean = s[0] * thread_inv_cnt;
+#pragma unroll
+        for (int j = 0; j < LDGS; ++j) {
+          const bool live = (j * TPR + t) < p.V;
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) {
+            const float d = live ? (xf[j][e] - mean) : 0.f;
+            q[0] += d * d;
+          }
+        }
+        group_moments<WARPS_N>(cnt, mean, q[0], red_smem[warp_m], phase, warp_m, warp_n, lane);
+      } else {
+        // Ragged rows (threads hold different element counts): the reference's two passes,
+        // mean first, then the centred sum of squares (layernorm.py:32-35).
+        group_sum<WARPS_N, 1>(s, red_smem[warp_m], phase, warp_m, warp_n, lane);
+        mean = s[0] * inv_n;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < LDGS; ++j)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) q[0] += xf[j][e] * xf[j][e];
+      group_sum<WARPS_N, 1>(q, red_smem[warp_m], phase, warp_m, warp_n, lane);
     }
-    float q[1] = {0.f};
-#pragma unroll
-    for (int j = 0; j < LDGS; ++j) {
-      const bool live = (j * TPR + t) < p.V;
-#pragma unroll
-      for (int e = 0; e < VEC; ++e) {
-        const float d = live ? (xf[j][e] - mean) : 0.f;
-        q[0] += d * d;
+    if (STAGES > 0) {
+      // Every thread of the group has its packets in registers: the slot can be refilled.
+      if (t == 0) {
+        const int64_t r = row + STAGES * step;
+        if (r < p.M) {
+          mbar_expect_tx(&bars[slot], row_bytes);
+          bulk_load(slots + (size_t)slot * row_bytes, xb + r * p.x_stride, row_bytes, &bars[slot]);
+        }
+      }
+      if (++slot == STAGES) {
+        slot = 0;
+        parity ^= 1u;
       }
     }
-    group_sum<WARPS_N, 1>(q, red_smem[warp_m], phase, warp_m, warp_n, lane);
+    if (!RMS && !uniform) {
+#pragma unroll
+      for (int j = 0; j < LDGS; ++j) {
+        const bool live = (j * TPR + t) < p.V;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          const float d = live ? (xf[j][e] - mean) : 0.f;
+          q[0] += d * d;
+        }
+      }
+      group_sum<WARPS_N, 1>(q, red_smem[warp_m], phase, warp_m, warp_n, lane);
+    }
     const float rstd = 1.f / sqrtf(q[0] * inv_n + p.eps);
     if (t == 0) {
       if (!RMS) p.mean[row] = mean;
@@ -122,6 +223,9 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32) norm_fwd_kernel(const F
       }
       if (v < p.V) st_stream(yrow + v, Pack16<T>::pack(yf));
     }
+  }
+  if (STAGES > 0) {
+    if (t == 0 && cta_abort) drain_ring<STAGES>(bars, first < p.M ? (p.M - first + step - 1) / step : 0);
   }
 }
 

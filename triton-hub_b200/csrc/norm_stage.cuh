@@ -1,0 +1,98 @@
+// Shared-memory row staging with bulk asynchronous copies (the TMA engine's 1-D form,
+// cp.async.bulk) completed on mbarriers.  Each row group owns a ring of STAGES slots; its
+// leader thread keeps the ring full, so STAGES rows per group are always in flight no matter
+// how few registers the consumers can spare.
+//
+// Every wait is bounded: a wait that runs out raises the CTA's abort flag and the device's
+// status word, after which all further waits in the CTA return at once.  The kernel then runs
+// to its normal end on whatever the slots hold (indices stay in range, so nothing faults) and
+// the host reports B200NORM_ERR_TIMEOUT from the status word.
+#pragma once
+
+#include "norm_common.cuh"
+
+namespace b200norm {
+
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait, far beyond any copy
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t arrivals) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals) : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_addr(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Bulk copy global -> this CTA's shared memory; both addresses and the size are multiples of 16.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_addr(smem_dst)),
+               "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar))
+               : "memory");
+}
+
+// Wait for `parity` of `bar`, giving up after kWaitLimitNs.  Returns false (and poisons the
+// CTA) on timeout or if the CTA is already poisoned.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* cta_abort, int* status) {
+  if (*cta_abort) return false;
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*cta_abort) return false;
+    if (global_ns() - t0 > kWaitLimitNs) {
+      *cta_abort = 1;
+      if (status != nullptr) *reinterpret_cast<volatile int*>(status) = 4;  // B200NORM_ERR_TIMEOUT
+      return false;
+    }
+  }
+}
+
+// Last step of a poisoned CTA: the leader of a row group gives the copies it issued (`count`
+// rows over STAGES slots) a bounded chance to land before the CTA's shared memory is released.
+template <int STAGES>
+__device__ __forceinline__ void drain_ring(uint64_t* bars, int64_t count) {
+  const unsigned long long t0 = global_ns();
+#pragma unroll
+  for (int s = 0; s < STAGES; ++s) {
+    if (count <= s) continue;
+    const int64_t fills = (count - s + STAGES - 1) / STAGES;
+    const uint32_t parity = static_cast<uint32_t>((fills - 1) & 1);
+    while (!mbar_try_wait(&bars[s], parity)) {
+      if (global_ns() - t0 > 10000000ull) return;  // 10 ms for the whole ring
+    }
+  }
+}
+
+__device__ __forceinline__ uint4 ld_shared16(const void* p) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(smem_addr(p)));
+  return v;
+}
+
+}  // namespace b200norm

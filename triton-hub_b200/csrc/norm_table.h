@@ -9,18 +9,20 @@ namespace b200norm {
 // is spread over `warps_n` warps, and a CTA runs `warps_m` such row groups side by side.
 struct PacketKernel {
   int ldgs, warps_m, warps_n;
+  int stages;          // shared-memory slots per row group filled by bulk copies (0: none)
   bool packet_params;  // re-reads weight / bias per row as 16-byte packets: they must be aligned
-  const void* fn[2];   // [0] LayerNorm, [1] RMSNorm
+  const void* fn;
   int capacity() const { return ldgs * 32 * warps_n; }  // packets per row it can hold
   int threads() const { return 32 * warps_m * warps_n; }
 };
 
 struct DTypeKernels {
   int elem_size;
-  const PacketKernel* fwd;  // ascending capacity
-  int n_fwd;
-  const PacketKernel* bwd;  // ascending capacity
-  int n_bwd;
+  // [0] LayerNorm, [1] RMSNorm; each table in ascending capacity
+  const PacketKernel* fwd[2];
+  int n_fwd[2];
+  const PacketKernel* bwd[2];
+  int n_bwd[2];
   const void* fwd_any[2];
   const void* bwd_dx_any[2];
   const void* bwd_dwdb_any[2];
