@@ -48,6 +48,9 @@ WORKLOADS = {
 TDTYPE = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16, "fp64": torch.float64}
 ESIZE = {"fp32": 4, "fp16": 2, "bf16": 2, "fp64": 8}
 FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes per row (dram__bytes_read.sum + dram__bytes_write.sum) of the backward kernel, from the
+# ncu captures summarised under profiles/ (taken at 16384 and 4096 rows; traffic is proportional to rows).
+NCU_BWD_DRAM_BYTES_PER_ROW = {"c2": 22413.0, "c4": 91160.0}
 
 
 def algorithmic_bytes(wl, rows):
@@ -160,14 +163,20 @@ def run_gpu(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
-    wl = WORKLOADS[args.workload]
+    wl = dict(WORKLOADS[args.workload])
+    if args.rows > 0:
+        wl["M"] = args.rows
+        wl["desc"] += f" cut to {args.rows} rows"
     ln = wl["op"] == "ln"
     total_rows = wl["M"] * (world if args.scaling == "weak" else 1)
     rows = total_rows // world
     N, eps = wl["N"], wl["eps"]
     x, dy, w, b = make_device_inputs(wl, rows, device, seed=1000 + rank)
     fwd_bytes, bwd_bytes = algorithmic_bytes(wl, rows)
-    side = torch.cuda.Stream(device=device) if world > 1 else None
+    exchange = None
+    if world > 1:
+        from b200norm.parallel import GradExchange, sharded_layernorm_bwd, sharded_rmsnorm_bwd
+        exchange = GradExchange(mode=args.exchange)
 
     def step(timing=None):
         """forward + backward; with world > 1 also starts the dweight/dbias all-reduce on the
@@ -183,17 +192,12 @@ def run_gpu(args):
         pending = None
         if world > 1:
             if ln:
-                dx, _, _, gs = Fn._layernorm_bwd(x, dy, w, b, mean, rstd, eps, group_sums=True,
-                                                 need_dw=False, need_db=False)
+                dx, pending = sharded_layernorm_bwd(x, dy, w, b, mean, rstd, eps, exchange)
             else:
-                dx, _, gs = Fn._rmsnorm_bwd(x, dy, w, rstd, eps, group_sums=True, need_dw=False)
+                dx, pending = sharded_rmsnorm_bwd(x, dy, w, rstd, eps, exchange)
             if timing is not None:
                 timing[2].record()
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                work = dist.all_reduce(gs, async_op=True)
-            pending = (work, gs)
-            out = (y, dx, gs)
+            out = (y, dx)
         else:
             if ln:
                 dx, dw, db = Fn._layernorm_bwd(x, dy, w, b, mean, rstd, eps)
@@ -209,9 +213,7 @@ def run_gpu(args):
         """Wait for an exchange and cast the reduced sums to the parameter type."""
         if pending is None:
             return None
-        work, gs = pending
-        work.wait()
-        return Fn.finalize_dwdb(gs, w.dtype)
+        return exchange.finish(pending, w.dtype)
 
     sampler = ClockSampler(local)
     sampler.start()
@@ -286,7 +288,8 @@ def run_gpu(args):
             "dim": N,
             "l2_policy": f"inputs larger than L2 ({(2 * rows * N * ESIZE[wl['dtype']]) >> 20} MiB of x+dy per GPU vs 126 MB)"
             if 2 * rows * N * ESIZE[wl["dtype"]] > 126e6 else "inputs fit in L2 (launch-bound case; GB/s not meaningful)",
-            "parallelism": f"rows sharded over {world} GPU(s); fp32 dweight/dbias all-reduce over NCCL" if world > 1
+            "parallelism": f"rows sharded over {world} GPU(s); fp32 dweight/dbias {args.exchange} over NCCL, "
+                           "overlapped with the next step's launches" if world > 1
             else "single GPU",
         },
         "rows_per_s": round(total_rows / (ms_per_step * 1e-3), 1),
@@ -300,7 +303,11 @@ def run_gpu(args):
             "peak": peak,
             "unit": "GB/s",
             "frac": round(bwd_gbs / peak, 4),
-            "traffic": None,
+            "traffic": (round(NCU_BWD_DRAM_BYTES_PER_ROW[args.workload] * rows)
+                        if args.workload in NCU_BWD_DRAM_BYTES_PER_ROW else None),
+            "traffic_source": ("ncu dram__bytes_read.sum + dram__bytes_write.sum of norm_bwd_kernel on a smaller case "
+                               "(profiles/), scaled by the row count; writes still dirty in L2 at kernel end are not in it"
+                               if args.workload in NCU_BWD_DRAM_BYTES_PER_ROW else None),
             "bytes_per_launch": bwd_bytes,
             "ms_per_launch": round(bwd_ms, 5),
             "fwd_kernel": {"achieved": round(fwd_gbs, 1), "frac": round(fwd_gbs / peak, 4),
@@ -468,8 +475,11 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--rows", type=int, default=0, help="override the workload's row count (profiling on a smaller case)")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--exchange", default="all_reduce", choices=["all_reduce", "all_gather"],
+                    help="multi-GPU dweight/dbias exchange (all_gather = bit-exact, G-invariant)")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-e2e", action="store_true")

@@ -1,0 +1,126 @@
+"""Row-sharded LayerNorm / RMSNorm across the GPUs of one box.
+
+Rows are independent, so each rank (one process per GPU) runs forward and backward on its own
+block of rows with no communication.  Only dweight / dbias are sums over ALL rows: every rank's
+backward call emits fp32 per-shard sums (``group_sums``), which are exchanged over
+torch.distributed (NCCL over NVLink) on a side stream while the caller goes on launching the
+next layer, and are then added and cast to the parameter dtype by ``finalize_dwdb``.
+
+The reference is single-GPU (no torch.distributed anywhere in TritonHub); this module is the
+data-parallel layer added on top of its `_layernorm_bwd` / `_rmsnorm_bwd`
+(TritonHub/Normalization/layernorm.py:155-209, rmsnorm.py:124-167).
+
+Two exchange modes:
+  "all_reduce"  one NCCL sum of the (slots, N) fp32 vector.  Equal to a single-GPU run up to fp32
+                rounding: the order of the cross-rank additions is NCCL's.
+  "all_gather"  every rank receives all shard sums and adds them left to right in global shard
+                order.  Bit-identical on every rank, for every run, and to a single-GPU run that
+                used the same total number of row shards.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import functional as Fn
+
+TOTAL_SHARDS = 8  # a box has 8 GPUs; 1, 2, 4 or 8 ranks each own 8 / world consecutive shards
+
+
+def shard_bounds(rows: int, world: int, rank: int) -> Tuple[int, int]:
+    """Contiguous block of rows owned by `rank`: [begin, end).  Rows must divide evenly."""
+    if rows % world != 0:
+        raise ValueError(f"{rows} rows do not divide over {world} ranks")
+    per = rows // world
+    return rank * per, (rank + 1) * per
+
+
+def local_row_shards(world: int, total_shards: int = TOTAL_SHARDS) -> int:
+    """Row shards each rank keeps apart so that all ranks together hold `total_shards`."""
+    if total_shards % world != 0:
+        raise ValueError(f"world size {world} does not divide {total_shards} row shards")
+    return total_shards // world
+
+
+class GradExchange:
+    """Cross-rank sum of the fp32 dweight / dbias shard sums of one backward call.
+
+    start(group_sums) enqueues the collective behind the work already on the current stream and
+    returns at once; finish(handle, dtype) makes the current stream wait for it and returns the
+    finished (dweight[, dbias]) in `dtype`.  Between the two the caller is free to launch more
+    kernels: they overlap the exchange.
+    """
+
+    def __init__(self, group: Optional[dist.ProcessGroup] = None, mode: str = "all_reduce",
+                 finalize: Callable[[torch.Tensor, torch.dtype], Sequence[torch.Tensor]] = Fn.finalize_dwdb):
+        if mode not in ("all_reduce", "all_gather"):
+            raise ValueError(f"unknown exchange mode {mode!r}")
+        self.group, self.mode, self.finalize = group, mode, finalize
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self._side = None
+
+    def _side_stream(self, device):
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=device)
+        return self._side
+
+    def start(self, group_sums: torch.Tensor):
+        """group_sums: (local_shards, slots, N) fp32, contiguous.  Returns an opaque handle."""
+        assert group_sums.dtype == torch.float32 and group_sums.dim() == 3 and group_sums.is_contiguous()
+        if self.world == 1:
+            return (None, group_sums)
+        if self.mode == "all_reduce":
+            # collapse this rank's shards first (left to right), then sum across ranks
+            local = group_sums if group_sums.shape[0] == 1 else None
+            buf = local if local is not None else torch.stack(self._fold(group_sums)).unsqueeze(0).contiguous()
+        else:
+            buf = torch.empty((self.world * group_sums.shape[0],) + tuple(group_sums.shape[1:]),
+                              dtype=torch.float32, device=group_sums.device)
+        if group_sums.is_cuda:
+            side = self._side_stream(group_sums.device)
+            side.wait_stream(torch.cuda.current_stream(group_sums.device))
+            with torch.cuda.stream(side):
+                work = self._collective(buf, group_sums)
+            # the buffers are used on the side stream: keep the allocator from recycling them early
+            buf.record_stream(side)
+            group_sums.record_stream(side)
+        else:
+            work = self._collective(buf, group_sums)
+        return (work, buf)
+
+    def _fold(self, group_sums):
+        """Left-to-right fp32 sum over this rank's shards, per slot (host-side glue for all_reduce)."""
+        acc = group_sums[0].clone()
+        for g in range(1, group_sums.shape[0]):
+            acc += group_sums[g]
+        return [acc[s] for s in range(acc.shape[0])]
+
+    def _collective(self, buf, group_sums):
+        if self.mode == "all_reduce":
+            return dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+        return dist.all_gather_into_tensor(buf, group_sums, group=self.group, async_op=True)
+
+    def finish(self, handle, w_dtype: torch.dtype):
+        """Wait for the exchange started by `start` and return the finished gradients."""
+        work, buf = handle
+        if work is not None:
+            work.wait()  # CUDA: a stream-side wait, the host does not block
+        return tuple(self.finalize(buf, w_dtype))
+
+
+def sharded_layernorm_bwd(x, dout, weight, bias, mean, rstd, eps, exchange: GradExchange):
+    """Backward of one rank's rows: returns (dx, handle); `exchange.finish(handle, weight.dtype)`
+    later yields the global (dweight, dbias)."""
+    shards = local_row_shards(exchange.world) if exchange.mode == "all_gather" else 1
+    dx, _, _, gs = Fn._layernorm_bwd(x, dout, weight, bias, mean, rstd, eps, row_shards=shards, group_sums=True,
+                                     need_dw=False, need_db=False)
+    return dx, exchange.start(gs)
+
+
+def sharded_rmsnorm_bwd(x, dout, weight, rstd, eps, exchange: GradExchange):
+    """RMSNorm twin of `sharded_layernorm_bwd`; `finish` yields (dweight,)."""
+    shards = local_row_shards(exchange.world) if exchange.mode == "all_gather" else 1
+    dx, _, gs = Fn._rmsnorm_bwd(x, dout, weight, rstd, eps, row_shards=shards, group_sums=True, need_dw=False)
+    return dx, exchange.start(gs)
