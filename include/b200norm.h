@@ -145,6 +145,38 @@ B200NORM_API int b200norm_rms_bwd(const void* x, int64_t x_row_stride, const voi
 B200NORM_API int b200norm_finalize_dwdb(const float* group_sums, int groups, int slots, void* dw, void* db, int64_t N,
                            int w_dtype, void* stream);
 
+/*
+ * RMSNorm backward for callers that cannot allocate device memory.  (No counterpart in the
+ * reference, whose wrapper allocates its partial-sum buffers with torch on every call.)
+ *
+ * b200norm_rms_bwd needs a caller-provided workspace for its fp32 dweight partial rows.  A host
+ * runtime that plans all of its device memory once at start-up -- an inference or training
+ * engine with a static memory planner, or a real-time loop that may not call cudaMalloc because
+ * it synchronises the device and can fail mid-run -- has no such buffer to hand over.  This
+ * variant computes the same dx and dweight with the partial rows kept in a fixed array of
+ * B200NORM_STATIC_SCRATCH_BYTES that is part of the library image: every GPU that loads
+ * libb200norm.so holds that much memory until the process exits.  The caller still passes x, dy,
+ * w, rstd, dx and dw.
+ *
+ *   - It calls no cudaMalloc / cudaFree / cudaHostAlloc and no allocating library routine.
+ *   - The first call on each device looks up the array's device address, the SM count and kernel
+ *     occupancies; make that first call before any stream capture.
+ *   - Shapes whose partial rows exceed B200NORM_STATIC_SCRATCH_BYTES (roughly: resident CTAs x N x
+ *     4 bytes, e.g. N = 16384 on a 148-SM GPU) are refused with B200NORM_ERR_UNSUPPORTED; use
+ *     b200norm_rms_bwd with a caller workspace for those.
+ *   - All calls on a device share the one array and it keeps the previous call's contents.
+ *     Nothing in it has to start at zero (each call overwrites every partial row it later reads),
+ *     but two calls that overlap on the GPU -- different streams, or different threads -- race
+ *     on it.  Serialise them.
+ *   - A bounded device-side wait that expires poisons only that launch; this variant has no
+ *     host-readable status word (b200norm_device_status covers the other entry points).
+ */
+#define B200NORM_STATIC_SCRATCH_BYTES (8u << 20)
+B200NORM_API int b200norm_rms_bwd_static(const void* x, int64_t x_row_stride, const void* dy,
+                                         int64_t dy_row_stride, const void* w, const float* rstd, void* dx,
+                                         int64_t dx_row_stride, void* dw, int64_t M, int64_t N, int io_dtype,
+                                         int w_dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,92 @@
+"""b200norm_rms_bwd_static: the RMSNorm backward entry point for hosts that cannot allocate.
+
+Some hosts of this library plan every byte of device memory at start-up (a serving or training
+engine with a static memory planner, a real-time loop that must never call cudaMalloc because it
+synchronises the device and may fail mid-run).  They cannot give b200norm_rms_bwd the per-call
+workspace it asks for, so this entry point keeps the fp32 dweight partial rows in an array that is
+part of the library image.  The test calls it through the C ABI twice in a row -- the second call
+finds the first call's partial rows still in the shared array -- and checks dx and dweight against
+the workspace-taking entry point within the parity bars used everywhere else in the suite.
+
+Collected last on purpose (file name): a run that stops at the first failure has then already
+run every other test.
+"""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from b200norm import _lib
+from helpers import TOL, assert_parity, to_numpy
+
+DEV = "cuda:0"
+CODE = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+NAME = {torch.float32: "fp32", torch.float16: "fp16", torch.bfloat16: "bf16"}
+
+
+def _inputs(M, N, dtype, seed):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    x = torch.randn(M, N, device=DEV, generator=g).to(dtype)
+    dy = torch.randn(M, N, device=DEV, generator=g).to(dtype)
+    w = (1 + 0.1 * torch.randn(N, device=DEV, generator=g)).to(dtype)
+    rstd = torch.rsqrt(x.float().pow(2).mean(-1) + 1e-6).contiguous()
+    return x, dy, w, rstd
+
+
+def _with_workspace(lib, x, dy, w, rstd):
+    M, N = x.shape
+    dx, dw = torch.empty_like(x), torch.empty_like(w)
+    nbytes = lib.b200norm_bwd_workspace_bytes(M, N, CODE[x.dtype], 1)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=DEV)
+    _lib.check(lib.b200norm_rms_bwd(x.data_ptr(), N, dy.data_ptr(), N, w.data_ptr(), rstd.data_ptr(),
+                                    dx.data_ptr(), N, dw.data_ptr(), None, 1, ws.data_ptr(), nbytes, M, N,
+                                    CODE[x.dtype], CODE[w.dtype], torch.cuda.current_stream().cuda_stream))
+    return dx, dw
+
+
+def _static(lib, x, dy, w, rstd):
+    M, N = x.shape
+    dx, dw = torch.empty_like(x), torch.empty_like(w)   # outputs are the caller's, as for every entry point
+    rc = lib.b200norm_rms_bwd_static(x.data_ptr(), N, dy.data_ptr(), N, w.data_ptr(), rstd.data_ptr(),
+                                     dx.data_ptr(), N, dw.data_ptr(), M, N, CODE[x.dtype], CODE[w.dtype],
+                                     torch.cuda.current_stream().cuda_stream)
+    return rc, dx, dw
+
+
+@pytest.mark.parametrize("dtype,M,N", [(torch.bfloat16, 3000, 4096), (torch.float32, 517, 1000),
+                                       (torch.float16, 64, 77)])
+def test_static_scratch_matches_workspace_entry_point_two_calls_in_a_row(dtype, M, N):
+    lib = _lib.load()
+    tol = TOL[NAME[dtype]]
+    with torch.cuda.device(0):
+        for call, seed in enumerate((11, 12)):     # second call: different data over the first call's leftovers
+            x, dy, w, rstd = _inputs(M, N, dtype, seed)
+            want_dx, want_dw = _with_workspace(lib, x, dy, w, rstd)
+            rc, dx, dw = _static(lib, x, dy, w, rstd)
+            _lib.check(rc)
+            torch.cuda.synchronize()
+            assert_parity(to_numpy(dx), to_numpy(want_dx), tol, f"call {call + 1}: dx")
+            assert_parity(to_numpy(dw), to_numpy(want_dw), tol, f"call {call + 1}: dw")
+            # same kernels, same launch plan, same fixed-order reduction: the results are in fact identical
+            assert torch.equal(dx, want_dx) and torch.equal(dw, want_dw)
+
+
+def test_shapes_beyond_the_built_in_scratch_are_refused_with_a_clear_error():
+    lib = _lib.load()
+    M, N = 4096, 16384          # 148+ partial rows x 16384 x 4 bytes > 8 MiB
+    with torch.cuda.device(0):
+        x, dy, w, rstd = _inputs(M, N, torch.bfloat16, 5)
+        rc, _, _ = _static(lib, x, dy, w, rstd)
+        assert rc == _lib.ERR_UNSUPPORTED
+        msg = lib.b200norm_last_error().decode()
+        assert "built-in scratch" in msg and "b200norm_rms_bwd" in msg
+        # dx alone needs no scratch at all and is still served
+        dx = torch.empty_like(x)
+        rc = lib.b200norm_rms_bwd_static(x.data_ptr(), N, dy.data_ptr(), N, w.data_ptr(), rstd.data_ptr(),
+                                         dx.data_ptr(), N, None, M, N, _lib.BF16, _lib.BF16,
+                                         torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc)
+        want_dx, _ = _with_workspace(lib, x, dy, w, rstd)
+        torch.cuda.synchronize()
+        assert torch.equal(dx, want_dx)

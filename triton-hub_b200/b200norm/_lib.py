@@ -34,6 +34,7 @@ SIGNATURES = {
     "b200norm_rms_bwd": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _int, _vp, _sz, _i64, _i64,
                                 _int, _int, _vp]),
     "b200norm_finalize_dwdb": (_int, [_vp, _int, _int, _vp, _vp, _i64, _int, _vp]),
+    "b200norm_rms_bwd_static": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _int, _int, _vp]),
 }
 
 _lock = threading.Lock()

@@ -275,6 +275,109 @@ int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, con
                 dim3(32, 16), 0, &c, stream);
 }
 
+// ---------------------------------------------------------------------------------------
+// RMSNorm backward with built-in scratch (b200norm_rms_bwd_static): for hosts that plan their
+// device memory once and cannot hand over, or allocate, a workspace per call.
+//
+// The dweight partial rows live in this file-scope device array instead of a caller buffer.
+// Every GPU that loads the library holds it until the process exits.  All calls on a device
+// share it and it keeps the last call's contents; nothing in it has to start at zero, because
+// each launch writes every partial row (all P of them, zero-row CTAs included) before the
+// column reduce reads them.  Calls that overlap on the GPU race on it.
+// ---------------------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = B200NORM_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+static __device__ int g_static_status;  // where this variant's kernels report an expired wait
+
+struct StaticState {
+  DeviceState dev;  // SM count and occupancy cache; no pinned status word is mapped for it
+  void* scratch = nullptr;
+};
+StaticState g_static[kMaxDevices];
+
+// Per-device set-up of the static variant, run by its first call on each device with that
+// device current.  In host code `g_static_scratch` names a host-side stand-in for the device
+// array, not a device address -- handing it to a kernel would fault, or quietly use the wrong
+// memory where the GPU can reach host memory -- so the address is asked for here, once.
+int static_state(StaticState** out) {
+  int d = -1;
+  cudaError_t e = cudaGetDevice(&d);
+  if (e != cudaSuccess) return fail(B200NORM_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (d < 0 || d >= kMaxDevices) return fail(B200NORM_ERR_CUDA, "device index %d out of range", d);
+  StaticState& s = g_static[d];
+  std::call_once(s.dev.once, [&]() {
+    s.dev.init_err = cudaDeviceGetAttribute(&s.dev.sm_count, cudaDevAttrMultiProcessorCount, d);
+    if (s.dev.init_err != cudaSuccess) return;
+    s.dev.init_err = cudaGetSymbolAddress(&s.scratch, g_static_scratch);
+    if (s.dev.init_err != cudaSuccess) return;
+    s.dev.init_err = cudaGetSymbolAddress(reinterpret_cast<void**>(&s.dev.status_dev), g_static_status);
+  });
+  if (s.dev.init_err != cudaSuccess)
+    return fail(B200NORM_ERR_CUDA, "static scratch set-up: %s", cudaGetErrorString(s.dev.init_err));
+  *out = &s;
+  return B200NORM_OK;
+}
+
+int rms_bwd_static_impl(const void* x, int64_t xs, const void* dy, int64_t dys, const void* w, const float* rstd,
+                        void* dx, int64_t dxs, void* dw, int64_t M, int64_t N, int io_dtype, int w_dtype,
+                        void* stream_v) {
+  if (int rc = check_common(M, N, io_dtype, w_dtype)) return rc;
+  if (M > 0 && (!x || !dy || !dx || !rstd)) return fail(B200NORM_ERR_ARG, "null x / dy / dx / rstd");
+  if (xs < N || dys < N || dxs < N) return fail(B200NORM_ERR_ARG, "row stride smaller than N");
+  if (M == 0 && dw == nullptr) return B200NORM_OK;
+  StaticState* st;
+  if (int rc = static_state(&st)) return rc;
+  const DTypeKernels* k = kernels_for(io_dtype);
+  const int es = k->elem_size;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+  const bool packets =
+      (N * es) % 16 == 0 && aligned16(x, xs, es) && aligned16(dy, dys, es) && aligned16(dx, dxs, es);
+  BwdPlan plan;
+  if (int rc = plan_bwd(st->dev, k, kRMS, M, N, packets, &plan)) return rc;
+  const int64_t P = plan.ctas_per_shard;
+  if (dw != nullptr && partial_bytes(P, N) > kStaticScratchBytes)
+    return fail(B200NORM_ERR_UNSUPPORTED,
+                "b200norm_rms_bwd_static: %zu bytes of dweight partial rows needed (%lld rows x N=%lld), the built-in "
+                "scratch holds %zu; use b200norm_rms_bwd with a caller workspace",
+                partial_bytes(P, N), (long long)P, (long long)N, kStaticScratchBytes);
+
+  BwdParams p;
+  p.x = x; p.dy = dy; p.w = w; p.mean = nullptr; p.rstd = rstd; p.dx = dx;
+  p.dw_part = (dw != nullptr) ? static_cast<float*>(st->scratch) : nullptr;
+  p.db_part = nullptr;
+  p.x_stride = xs; p.dy_stride = dys; p.dx_stride = dxs;
+  p.M = M; p.rows_per_shard = M; p.ctas_per_shard = plan.ctas_per_shard;
+  p.N = static_cast<int>(N); p.V = static_cast<int>(N * es / 16); p.w_dtype = w_dtype;
+  p.status = st->dev.status_dev;
+
+  if (plan.pk != nullptr) {
+    if (int rc = launch(plan.pk->fn, dim3(static_cast<unsigned>(P)), dim3(plan.pk->threads()), plan.smem, &p, stream))
+      return rc;
+  } else {
+    if (M > 0) {
+      int occ;
+      if (int rc = occupancy(st->dev, k->bwd_dx_any[kRMS], 256, 0, &occ)) return rc;
+      const int grid = static_cast<int>(std::min<int64_t>(M, (int64_t)st->dev.sm_count * occ));
+      if (int rc = launch(k->bwd_dx_any[kRMS], dim3(grid), dim3(256), 0, &p, stream)) return rc;
+    }
+    if (dw != nullptr) {
+      const dim3 grid(static_cast<unsigned>((N + 255) / 256), static_cast<unsigned>(P));
+      if (int rc = launch(k->bwd_dwdb_any[kRMS], grid, dim3(256), 0, &p, stream)) return rc;
+    }
+  }
+  if (dw == nullptr) return B200NORM_OK;
+
+  ColReduceParams c;
+  c.part[0] = p.dw_part; c.part[1] = nullptr;
+  c.out[0] = dw; c.out[1] = nullptr;
+  c.group_sums = nullptr;
+  c.per_shard = plan.ctas_per_shard; c.row_shards = 1; c.slots = 1;
+  c.N = static_cast<int>(N); c.w_dtype = w_dtype;
+  return launch(reinterpret_cast<const void*>(&colreduce_kernel), dim3(static_cast<unsigned>((N + 31) / 32), 1),
+                dim3(32, 16), 0, &c, stream);
+}
+
 }  // namespace
 }  // namespace b200norm
 
@@ -359,6 +462,13 @@ int b200norm_finalize_dwdb(const float* group_sums, int groups, int slots, void*
   p.groups = groups; p.slots = slots; p.N = static_cast<int>(N); p.w_dtype = w_dtype;
   return launch(reinterpret_cast<const void*>(&finalize_kernel), dim3(static_cast<unsigned>((N + 255) / 256), slots),
                 dim3(256), 0, &p, static_cast<cudaStream_t>(stream));
+}
+
+int b200norm_rms_bwd_static(const void* x, int64_t x_row_stride, const void* dy, int64_t dy_row_stride,
+                            const void* w, const float* rstd, void* dx, int64_t dx_row_stride, void* dw, int64_t M,
+                            int64_t N, int io_dtype, int w_dtype, void* stream) {
+  return rms_bwd_static_impl(x, x_row_stride, dy, dy_row_stride, w, rstd, dx, dx_row_stride, dw, M, N, io_dtype,
+                             w_dtype, stream);
 }
 
 }  // extern "C"
