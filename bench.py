@@ -174,9 +174,12 @@ def run_gpu(args):
     x, dy, w, b = make_device_inputs(wl, rows, device, seed=1000 + rank)
     fwd_bytes, bwd_bytes = algorithmic_bytes(wl, rows)
     exchange = None
+    wl_n = WORKLOADS[args.workload]["N"]
     if world > 1:
-        from b200norm.parallel import GradExchange, sharded_layernorm_bwd, sharded_rmsnorm_bwd
-        exchange = GradExchange(mode=args.exchange)
+        from b200norm.parallel import GradExchange, PushExchange, sharded_layernorm_bwd, sharded_rmsnorm_bwd
+        exchange = (PushExchange(max_n=wl_n, slots=2, device=device, total_shards=8 if args.g_invariant else None)
+                    if args.exchange == "push"
+                    else GradExchange(mode=args.exchange))
 
     def step(timing=None):
         """forward + backward; with world > 1 also starts the dweight/dbias all-reduce on the
@@ -191,7 +194,10 @@ def run_gpu(args):
             timing[1].record()
         pending = None
         if world > 1:
-            if ln:
+            if args.exchange == "push":
+                dx, pending = (exchange.backward_layernorm(x, dy, w, b, mean, rstd, eps) if ln
+                               else exchange.backward_rmsnorm(x, dy, w, rstd, eps))
+            elif ln:
                 dx, pending = sharded_layernorm_bwd(x, dy, w, b, mean, rstd, eps, exchange)
             else:
                 dx, pending = sharded_rmsnorm_bwd(x, dy, w, rstd, eps, exchange)
@@ -288,8 +294,11 @@ def run_gpu(args):
             "dim": N,
             "l2_policy": f"inputs larger than L2 ({(2 * rows * N * ESIZE[wl['dtype']]) >> 20} MiB of x+dy per GPU vs 126 MB)"
             if 2 * rows * N * ESIZE[wl["dtype"]] > 126e6 else "inputs fit in L2 (launch-bound case; GB/s not meaningful)",
-            "parallelism": f"rows sharded over {world} GPU(s); fp32 dweight/dbias {args.exchange} over NCCL, "
-                           "overlapped with the next step's launches" if world > 1
+            "parallelism": (f"rows sharded over {world} GPU(s); fp32 dweight/dbias exchange: "
+                            + ("column reduce fused with a push into every rank's inbox over NVLink peer memory, "
+                               "finished one step later" if args.exchange == "push"
+                               else f"NCCL {args.exchange} on a side stream, overlapped with the next step's launches"))
+            if world > 1
             else "single GPU",
         },
         "rows_per_s": round(total_rows / (ms_per_step * 1e-3), 1),
@@ -478,8 +487,12 @@ def main():
     ap.add_argument("--rows", type=int, default=0, help="override the workload's row count (profiling on a smaller case)")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--exchange", default="all_reduce", choices=["all_reduce", "all_gather"],
-                    help="multi-GPU dweight/dbias exchange (all_gather = bit-exact, G-invariant)")
+    ap.add_argument("--g-invariant", action="store_true",
+                    help="push exchange over 8 fixed row shards: dweight/dbias bit-identical for any GPU count")
+    ap.add_argument("--exchange", default="push", choices=["push", "all_reduce", "all_gather"],
+                    help="multi-GPU dweight/dbias exchange: push = column reduce fused with stores into every "
+                         "rank's inbox over NVLink peer memory (bit-exact, G-invariant); all_reduce / all_gather = "
+                         "NCCL collectives on a side stream")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-e2e", action="store_true")

@@ -146,6 +146,49 @@ B200NORM_API int b200norm_finalize_dwdb(const float* group_sums, int groups, int
                            int w_dtype, void* stream);
 
 /*
+ * Multi-GPU exchange fused into the backward's column reduce.  (No counterpart in the reference,
+ * which is single-GPU.)  One process per GPU; every rank owns an inbox of `depth` equal slots of
+ * inbox_bytes / depth each -- a slot holds one exchange's (total_shards, slots, N) fp32 at its
+ * start -- and a flag array (depth, world) u64, in memory that is
+ * peer-mapped into all ranks (CUDA IPC / VMM -- torch.distributed._symmetric_memory provides it).
+ *
+ * b200norm_*_bwd_push: like b200norm_*_bwd, but instead of writing dw / db the column-reduce
+ *   kernel stores this rank's fp32 shard sums directly into slot `seq % depth` of EVERY rank's
+ *   inbox (plain stores over NVLink, no loads from remote memory) and then raises this rank's
+ *   flag on every rank to `seq`.  This rank fills shards [rank*row_shards, (rank+1)*row_shards);
+ *   world * row_shards must equal peers->total_shards.
+ * b200norm_finalize_pushed: waits (bounded, 2 s) until all `world` flags of slot `seq % depth`
+ *   have reached `seq`, then adds the total_shards sums left to right in fp32 and casts to
+ *   w_dtype.  Same bits on every rank and as a single GPU summing the same shards.
+ *
+ * `seq` starts at 1 and grows by 1 per exchange on all ranks alike.  A rank must finish
+ * exchange s before it starts exchange s + depth - 1 (depth >= 3), which keeps a slot from being
+ * overwritten before a slower rank has read it.  inbox, flags and counter must be zero before
+ * the first exchange.
+ */
+#define B200NORM_MAX_PEERS 8
+typedef struct b200norm_peers {
+  int world, rank, depth, total_shards;
+  size_t inbox_bytes;                   /* size of each rank's inbox */
+  void* inbox[B200NORM_MAX_PEERS];      /* inbox[r]: rank r's inbox as mapped in THIS process */
+  void* flags[B200NORM_MAX_PEERS];      /* flags[r]: rank r's (depth, world) u64 flags, likewise */
+  void* counter;                        /* this rank's own (depth,) u32 scratch */
+} b200norm_peers;
+
+B200NORM_API int b200norm_ln_bwd_push(const void* x, int64_t x_row_stride, const void* dy, int64_t dy_row_stride,
+                                      const void* w, const float* mean, const float* rstd, void* dx,
+                                      int64_t dx_row_stride, int row_shards, void* workspace,
+                                      size_t workspace_bytes, int64_t M, int64_t N, int io_dtype, int w_dtype,
+                                      const b200norm_peers* peers, uint64_t seq, void* stream);
+B200NORM_API int b200norm_rms_bwd_push(const void* x, int64_t x_row_stride, const void* dy, int64_t dy_row_stride,
+                                       const void* w, const float* rstd, void* dx, int64_t dx_row_stride,
+                                       int row_shards, void* workspace, size_t workspace_bytes, int64_t M,
+                                       int64_t N, int io_dtype, int w_dtype, const b200norm_peers* peers,
+                                       uint64_t seq, void* stream);
+B200NORM_API int b200norm_finalize_pushed(const b200norm_peers* peers, uint64_t seq, int slots, void* dw, void* db,
+                                          int64_t N, int w_dtype, void* stream);
+
+/*
  * RMSNorm backward for callers that cannot allocate device memory.  (No counterpart in the
  * reference, whose wrapper allocates its partial-sum buffers with torch on every call.)
  *

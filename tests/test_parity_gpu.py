@@ -214,6 +214,93 @@ def test_row_shards_equal_separate_launches_bit_for_bit(rms):
     assert torch.equal(torch.cat(dxs, 0), dx)
 
 
+@pytest.mark.parametrize("rms", [False, True])
+@pytest.mark.parametrize("world", [1, 4])
+def test_fused_push_exchange_emulated_on_one_gpu(rms, world):
+    """The column reduce that pushes shard sums into every rank's inbox, with the ranks emulated as
+    consecutive launches on one GPU (each 'rank' has its own inbox, flags and counter; a flag is
+    always set by an earlier launch before a finish kernel looks at it, so nothing waits).  Every
+    rank's finished dweight / dbias must equal the single-launch 8-shard result bit for bit, over
+    several exchanges that reuse the inbox slots."""
+    import ctypes
+    M, N, S, depth = 8 * 300, 2048, 8, 4
+    slots = 1 if rms else 2
+    lib = _lib.load()
+    inbox_bytes = depth * S * slots * N * 4
+    bufs = [torch.zeros(inbox_bytes + 256 * depth, dtype=torch.uint8, device=DEV) for _ in range(world)]
+    counters = [torch.zeros(depth, dtype=torch.int32, device=DEV) for _ in range(world)]
+    peers = []
+    for r in range(world):
+        pr = _lib.Peers()
+        pr.world, pr.rank, pr.depth, pr.total_shards, pr.inbox_bytes = world, r, depth, S, inbox_bytes
+        for q in range(world):
+            pr.inbox[q] = bufs[q].data_ptr()
+            pr.flags[q] = bufs[q].data_ptr() + inbox_bytes
+        pr.counter = counters[r].data_ptr()
+        peers.append(pr)
+    per = M // world
+    for seq in range(1, 7):       # more exchanges than inbox slots
+        if seq == 4:              # an exchange of another shape in between must not disturb the slots
+            N = 1024
+        x, dy, w, b = make_inputs(M, N, "bf16", seed=seq, has_b=not rms)
+        xt, dyt, wt, bt = (to_torch(a, "bf16", DEV) for a in (x, dy, w, b))
+        if rms:
+            _, rstd = Fn._rmsnorm_fwd(xt, wt, 1e-6)
+            dx1, dw1 = Fn._rmsnorm_bwd(xt, dyt, wt, rstd, 1e-6, row_shards=S)
+        else:
+            _, mean, rstd = Fn._layernorm_fwd(xt, wt, bt, 1e-6)
+            dx1, dw1, db1 = Fn._layernorm_bwd(xt, dyt, wt, bt, mean, rstd, 1e-6, row_shards=S)
+        for r in range(world):
+            sl = slice(r * per, (r + 1) * per)
+            push = (ctypes.byref(peers[r]), seq)
+            if rms:
+                dx, _ = Fn._rmsnorm_bwd(xt[sl], dyt[sl], wt, rstd[sl], 1e-6, row_shards=S // world, need_dw=False,
+                                        push=push)
+            else:
+                dx, _, _ = Fn._layernorm_bwd(xt[sl], dyt[sl], wt, bt, mean[sl], rstd[sl], 1e-6,
+                                             row_shards=S // world, need_dw=False, need_db=False, push=push)
+            assert torch.equal(dx, dx1[sl])
+        for r in range(world):
+            outs = Fn.finalize_pushed(ctypes.byref(peers[r]), seq, slots, N, torch.bfloat16, torch.device(DEV))
+            assert torch.equal(outs[0], dw1), f"rank {r} seq {seq}: dweight differs"
+            if not rms:
+                assert torch.equal(outs[1], db1), f"rank {r} seq {seq}: dbias differs"
+    torch.cuda.synchronize()
+    with torch.cuda.device(0):
+        assert lib.b200norm_device_status(0) == 0
+
+
+def test_finish_kernel_gives_up_on_a_flag_nobody_sets():
+    """A bounded wait that runs out: the finish kernel is asked for an exchange that no rank has
+    pushed.  It must return (after its 2 s limit), leave the context usable and raise the device
+    status word -- the host-visible form of a peer that never arrived."""
+    import ctypes
+    import time
+    N, depth, S = 256, 4, 8
+    lib = _lib.load()
+    inbox_bytes = depth * S * 1 * N * 4
+    buf = torch.zeros(inbox_bytes + 256 * depth, dtype=torch.uint8, device=DEV)
+    counter = torch.zeros(depth, dtype=torch.int32, device=DEV)
+    pr = _lib.Peers()
+    pr.world, pr.rank, pr.depth, pr.total_shards, pr.inbox_bytes = 1, 0, depth, S, inbox_bytes
+    pr.inbox[0], pr.flags[0], pr.counter = buf.data_ptr(), buf.data_ptr() + inbox_bytes, counter.data_ptr()
+    with torch.cuda.device(0):
+        assert lib.b200norm_device_status(1) == 0
+        t0 = time.time()
+        (dw,) = Fn.finalize_pushed(ctypes.byref(pr), 5, 1, N, torch.float32, torch.device(DEV))
+        torch.cuda.synchronize()
+        waited = time.time() - t0
+        assert 1.0 < waited < 10.0
+        assert lib.b200norm_device_status(1) == _lib.ERR_TIMEOUT     # read and cleared
+        assert lib.b200norm_device_status(0) == 0
+        # the context is still usable
+        assert torch.all(dw == 0)
+        x = torch.randn(8, N, device=DEV)
+        y, _ = Fn._rmsnorm_fwd(x, None, 1e-6)
+        torch.cuda.synchronize()
+        assert torch.isfinite(y).all()
+
+
 def test_outputs_do_not_write_out_of_bounds():
     """Canaries either side of y / dx / mean / rstd survive (the row-strided output path)."""
     N, M = 1000, 53

@@ -20,6 +20,18 @@ F32, F16, BF16, F64 = range(4)
 _c = ctypes
 _vp, _i64, _int, _f32, _sz = _c.c_void_p, _c.c_int64, _c.c_int, _c.c_float, _c.c_size_t
 
+MAX_PEERS = 8
+
+
+class Peers(ctypes.Structure):
+    """struct b200norm_peers: where the fused column reduce pushes shard sums (see b200norm.h)."""
+    _fields_ = [("world", _int), ("rank", _int), ("depth", _int), ("total_shards", _int),
+                ("inbox_bytes", _sz), ("inbox", _vp * MAX_PEERS), ("flags", _vp * MAX_PEERS),
+                ("counter", _vp)]
+
+
+_pp, _u64 = _c.POINTER(Peers), _c.c_uint64
+
 # name -> (restype, argtypes): every symbol include/b200norm.h declares.
 SIGNATURES = {
     "b200norm_version": (_int, []),
@@ -34,6 +46,11 @@ SIGNATURES = {
     "b200norm_rms_bwd": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _int, _vp, _sz, _i64, _i64,
                                 _int, _int, _vp]),
     "b200norm_finalize_dwdb": (_int, [_vp, _int, _int, _vp, _vp, _i64, _int, _vp]),
+    "b200norm_ln_bwd_push": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _int, _vp, _sz, _i64, _i64, _int,
+                                    _int, _pp, _u64, _vp]),
+    "b200norm_rms_bwd_push": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _int, _vp, _sz, _i64, _i64, _int, _int,
+                                     _pp, _u64, _vp]),
+    "b200norm_finalize_pushed": (_int, [_pp, _u64, _int, _vp, _vp, _i64, _int, _vp]),
     "b200norm_rms_bwd_static": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _int, _int, _vp]),
 }
 

@@ -117,7 +117,7 @@ def _rmsnorm_fwd(x, weight, eps):
     return out.reshape(*batch_shape, N), rstd
 
 
-def _bwd_common(op, x, dout, weight, bias, mean, rstd, row_shards, want_group_sums, need_dw, need_db):
+def _bwd_common(op, x, dout, weight, bias, mean, rstd, row_shards, want_group_sums, need_dw, need_db, push=None):
     _require_cuda(x)
     batch_shape = x.shape[:-1]
     x = _rows(x)
@@ -137,13 +137,25 @@ def _bwd_common(op, x, dout, weight, bias, mean, rstd, row_shards, want_group_su
     lib = _lib.load()
     with torch.cuda.device(x.device.index):
         ws, ws_bytes = None, 0
-        if dw is not None or db is not None or gs is not None:
+        if dw is not None or db is not None or gs is not None or push is not None:
             ws_bytes = lib.b200norm_bwd_workspace_bytes(M, N, _code(x, "input"), row_shards)
             if ws_bytes == 0:
                 _lib.check(_lib.ERR_ARG)
             ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=x.device)
         stream = torch.cuda.current_stream().cuda_stream
-        if op == "ln":
+        if push is not None:  # (Peers struct, sequence number): shard sums go to every rank's inbox
+            peers, seq = push
+            if op == "ln":
+                status = lib.b200norm_ln_bwd_push(
+                    x.data_ptr(), _row_stride(x), dout.data_ptr(), _row_stride(dout), _ptr(weight),
+                    mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(), N, row_shards, _ptr(ws), ws_bytes, M, N,
+                    _code(x, "input"), wcode, peers, seq, stream)
+            else:
+                status = lib.b200norm_rms_bwd_push(
+                    x.data_ptr(), _row_stride(x), dout.data_ptr(), _row_stride(dout), _ptr(weight),
+                    rstd.data_ptr(), dx.data_ptr(), N, row_shards, _ptr(ws), ws_bytes, M, N,
+                    _code(x, "input"), wcode, peers, seq, stream)
+        elif op == "ln":
             status = lib.b200norm_ln_bwd(
                 x.data_ptr(), _row_stride(x), dout.data_ptr(), _row_stride(dout), _ptr(weight),
                 mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(), N, _ptr(dw), _ptr(db), _ptr(gs),
@@ -158,21 +170,22 @@ def _bwd_common(op, x, dout, weight, bias, mean, rstd, row_shards, want_group_su
 
 
 def _layernorm_bwd(x, dout, weight, bias, mean, rstd, eps, *, row_shards=1, group_sums=False,
-                   need_dw=True, need_db=True):
+                   need_dw=True, need_db=True, push=None):
     """LayerNorm backward; returns (dx, dweight, dbias), the last two in the parameters' dtype
     (None for a missing parameter).  With ``group_sums=True`` a fourth value is returned: the
     fp32 (row_shards, 2, N) dweight/dbias sums per row shard, for a multi-GPU exchange.
-    ``eps`` is accepted and unused, as in the reference."""
+    ``eps`` is accepted and unused, as in the reference.  ``push=(peers, seq)`` sends the shard sums
+    to every rank's inbox instead (b200norm_ln_bwd_push); pass need_dw=need_db=False with it."""
     dx, dw, db, gs = _bwd_common("ln", x, dout, weight, bias, mean, rstd, row_shards, group_sums,
-                                 need_dw, need_db)
+                                 need_dw, need_db, push)
     return (dx, dw, db, gs) if group_sums else (dx, dw, db)
 
 
-def _rmsnorm_bwd(x, dout, weight, rstd, eps, *, row_shards=1, group_sums=False, need_dw=True):
+def _rmsnorm_bwd(x, dout, weight, rstd, eps, *, row_shards=1, group_sums=False, need_dw=True, push=None):
     """RMSNorm backward; returns (dx, dweight) and, with ``group_sums=True``, the fp32
     (row_shards, 1, N) per-shard dweight sums."""
     dx, dw, _, gs = _bwd_common("rms", x, dout, weight, None, None, rstd, row_shards, group_sums,
-                                need_dw, False)
+                                need_dw, False, push)
     return (dx, dw, gs) if group_sums else (dx, dw)
 
 
@@ -190,6 +203,18 @@ def finalize_dwdb(group_sums: torch.Tensor, w_dtype: torch.dtype):
             group_sums.data_ptr(), groups, slots, outs[0].data_ptr(),
             outs[1].data_ptr() if slots == 2 else None, N, code,
             torch.cuda.current_stream().cuda_stream))
+    return tuple(outs)
+
+
+def finalize_pushed(peers, seq, slots, N, w_dtype, device):
+    """dweight (and dbias) of exchange `seq` from this rank's inbox, once every rank has pushed
+    (b200norm_finalize_pushed; the wait happens on the GPU, bounded)."""
+    outs = [torch.empty((N,), dtype=w_dtype, device=device) for _ in range(slots)]
+    lib = _lib.load()
+    with torch.cuda.device(device):
+        _lib.check(lib.b200norm_finalize_pushed(
+            peers, seq, slots, outs[0].data_ptr(), outs[1].data_ptr() if slots == 2 else None, N,
+            _DTYPE_CODE[w_dtype], torch.cuda.current_stream().cuda_stream))
     return tuple(outs)
 
 

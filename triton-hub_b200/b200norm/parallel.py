@@ -10,7 +10,13 @@ The reference is single-GPU (no torch.distributed anywhere in TritonHub); this m
 data-parallel layer added on top of its `_layernorm_bwd` / `_rmsnorm_bwd`
 (TritonHub/Normalization/layernorm.py:155-209, rmsnorm.py:124-167).
 
-Two exchange modes:
+Three exchange paths:
+  PushExchange  the library's own: the backward's column-reduce kernel stores its shard sums
+                straight into every rank's inbox over NVLink peer memory and raises a flag; a
+                later finish kernel adds them left to right.  No collective-library kernel has to
+                be co-resident with the persistent forward / backward grids, and the result is
+                bit-identical across ranks, runs and GPU counts.  This is the default.
+  GradExchange  over torch.distributed collectives, in one of two modes:
   "all_reduce"  one NCCL sum of the (slots, N) fp32 vector.  Equal to a single-GPU run up to fp32
                 rounding: the order of the cross-rank additions is NCCL's.
   "all_gather"  every rank receives all shard sums and adds them left to right in global shard
@@ -24,6 +30,7 @@ from typing import Callable, Optional, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
+from . import _lib
 from . import functional as Fn
 
 TOTAL_SHARDS = 8  # a box has 8 GPUs; 1, 2, 4 or 8 ranks each own 8 / world consecutive shards
@@ -124,3 +131,91 @@ def sharded_rmsnorm_bwd(x, dout, weight, rstd, eps, exchange: GradExchange):
     shards = local_row_shards(exchange.world) if exchange.mode == "all_gather" else 1
     dx, _, gs = Fn._rmsnorm_bwd(x, dout, weight, rstd, eps, row_shards=shards, group_sums=True, need_dw=False)
     return dx, exchange.start(gs)
+
+
+class PushExchange:
+    """dweight / dbias exchange fused into the backward's column reduce (b200norm_*_bwd_push).
+
+    Each rank owns an inbox (depth, total_shards, slots, max_n) fp32 plus a flag array in
+    symmetric memory (torch.distributed._symmetric_memory: CUDA VMM allocations mapped into every
+    rank of the group).  `backward_*` launches the backward whose column reduce pushes this
+    rank's shard sums to all ranks; `finish` launches the kernel that waits (on the GPU, bounded)
+    for everyone's flags and adds the shards left to right.  Nothing blocks the host.
+
+    A rank may run at most `depth - 2` exchanges ahead of its oldest unfinished one.
+    """
+
+    def __init__(self, max_n: int, slots: int = 2, group: Optional[dist.ProcessGroup] = None,
+                 total_shards: Optional[int] = None, depth: int = 4, device: Optional[torch.device] = None):
+        self.group = group if group is not None else (dist.group.WORLD if dist.is_initialized() else None)
+        self.world = dist.get_world_size(self.group) if self.group is not None else 1
+        self.rank = dist.get_rank(self.group) if self.group is not None else 0
+        if self.world > _lib.MAX_PEERS:
+            raise ValueError(f"at most {_lib.MAX_PEERS} ranks (one box)")
+        # total_shards = world (default): one shard per rank, the fastest launch shape; results are
+        # identical on all ranks and from run to run.  total_shards = 8: additionally identical to
+        # a run on any other GPU count (and to one GPU using row_shards=8), at the cost of 8 / world
+        # times as many, shorter-lived CTAs in the backward.
+        total_shards = self.world if total_shards is None else total_shards
+        self.local_shards = local_row_shards(self.world, total_shards)
+        self.total_shards, self.depth, self.slots, self.max_n = total_shards, depth, slots, max_n
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.inbox_bytes = depth * total_shards * slots * max_n * 4
+        flag_bytes = (depth * max(self.world, 1) * 8 + 255) // 256 * 256
+        self._seq = 0
+        self._oldest_open = 1
+        self.counter = torch.zeros(depth, dtype=torch.int32, device=self.device)
+        if self.world == 1:
+            self._buf = torch.zeros(self.inbox_bytes + flag_bytes, dtype=torch.uint8, device=self.device)
+            bases = [self._buf.data_ptr()]
+        else:
+            import torch.distributed._symmetric_memory as symm_mem
+            self._buf = symm_mem.empty(self.inbox_bytes + flag_bytes, dtype=torch.uint8, device=self.device)
+            self._buf.zero_()
+            self._hdl = symm_mem.rendezvous(self._buf, self.group)
+            bases = [int(p) for p in self._hdl.buffer_ptrs]
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)  # every inbox and flag array is zero before anyone pushes
+        self.peers = _lib.Peers()
+        self.peers.world, self.peers.rank = self.world, self.rank
+        self.peers.depth, self.peers.total_shards = depth, total_shards
+        self.peers.inbox_bytes = self.inbox_bytes
+        for r in range(self.world):
+            self.peers.inbox[r] = bases[r]
+            self.peers.flags[r] = bases[r] + self.inbox_bytes
+        self.peers.counter = self.counter.data_ptr()
+
+    def _next(self, slots, N):
+        if N > self.max_n or slots > self.slots:
+            raise ValueError(f"exchange of {slots} x {N} exceeds this PushExchange ({self.slots} x {self.max_n})")
+        if self._seq + 1 - self._oldest_open > self.depth - 2:
+            raise RuntimeError("too many exchanges in flight: finish() an older one first")
+        self._seq += 1
+        return self._seq
+
+    def backward_layernorm(self, x, dout, weight, bias, mean, rstd, eps):
+        """This rank's rows: returns (dx, handle); finish(handle, dtype) yields (dweight, dbias)."""
+        N = x.shape[-1]
+        seq = self._next(2, N)
+        dx, _, _ = Fn._layernorm_bwd(x, dout, weight, bias, mean, rstd, eps, row_shards=self.local_shards,
+                                     need_dw=False, need_db=False, push=(ctypes_ref(self.peers), seq))
+        return dx, (seq, 2, N)
+
+    def backward_rmsnorm(self, x, dout, weight, rstd, eps):
+        """RMSNorm twin; finish yields (dweight,)."""
+        N = x.shape[-1]
+        seq = self._next(1, N)
+        dx, _ = Fn._rmsnorm_bwd(x, dout, weight, rstd, eps, row_shards=self.local_shards, need_dw=False,
+                                push=(ctypes_ref(self.peers), seq))
+        return dx, (seq, 1, N)
+
+    def finish(self, handle, w_dtype: torch.dtype):
+        seq, slots, N = handle
+        out = Fn.finalize_pushed(ctypes_ref(self.peers), seq, slots, N, w_dtype, self.device)
+        self._oldest_open = max(self._oldest_open, seq + 1)
+        return out
+
+
+def ctypes_ref(struct):
+    import ctypes
+    return ctypes.byref(struct)

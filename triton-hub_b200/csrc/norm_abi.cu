@@ -14,6 +14,7 @@
 #include "norm_bwd.cuh"
 #include "norm_colreduce.cuh"
 #include "norm_fwd.cuh"
+#include "norm_push.cuh"
 #include "norm_table.h"
 
 namespace b200norm {
@@ -203,18 +204,52 @@ size_t partial_bytes(int64_t P, int64_t N) {
   return (static_cast<size_t>(P) * N * sizeof(float) + 255) & ~static_cast<size_t>(255);
 }
 
+int check_peers(const b200norm_peers* peers, uint64_t seq, int slots, int64_t N, int row_shards) {
+  if (peers->world < 1 || peers->world > B200NORM_MAX_PEERS || peers->rank < 0 || peers->rank >= peers->world)
+    return fail(B200NORM_ERR_ARG, "peers: bad world / rank (%d / %d)", peers->world, peers->rank);
+  if (peers->depth < 3) return fail(B200NORM_ERR_ARG, "peers: depth must be >= 3 (got %d)", peers->depth);
+  if (seq == 0) return fail(B200NORM_ERR_ARG, "peers: sequence numbers start at 1");
+  if (row_shards >= 1 && peers->world * row_shards != peers->total_shards)
+    return fail(B200NORM_ERR_ARG, "peers: world %d x row_shards %d != total_shards %d", peers->world, row_shards,
+                peers->total_shards);
+  // each of the `depth` slots is inbox_bytes / depth and must hold (total_shards, slots, N) fp32
+  const size_t need = static_cast<size_t>(peers->depth) * peers->total_shards * slots * N * sizeof(float);
+  if (need > peers->inbox_bytes || peers->inbox_bytes % (sizeof(float) * peers->depth) != 0)
+    return fail(B200NORM_ERR_ARG, "peers: inbox holds %zu bytes, this exchange needs %zu", peers->inbox_bytes, need);
+  if (peers->counter == nullptr) return fail(B200NORM_ERR_ARG, "peers: null counter");
+  for (int r = 0; r < peers->world; ++r)
+    if (peers->inbox[r] == nullptr || peers->flags[r] == nullptr)
+      return fail(B200NORM_ERR_ARG, "peers: null inbox / flags for rank %d", r);
+  return B200NORM_OK;
+}
+
+PeerTargets peer_targets(const b200norm_peers* peers) {
+  PeerTargets t;
+  for (int r = 0; r < kMaxPeers; ++r) {
+    t.inbox[r] = (r < peers->world) ? static_cast<float*>(peers->inbox[r]) : nullptr;
+    t.flags[r] = (r < peers->world) ? static_cast<unsigned long long*>(peers->flags[r]) : nullptr;
+  }
+  t.counter = static_cast<unsigned int*>(peers->counter);
+  t.world = peers->world; t.rank = peers->rank; t.depth = peers->depth; t.total_shards = peers->total_shards;
+  t.slot_floats = peers->inbox_bytes / sizeof(float) / peers->depth;
+  return t;
+}
+
 int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, const void* w, const float* mean,
              const float* rstd, void* dx, int64_t dxs, void* dw, void* db, float* group_sums, int row_shards,
              void* workspace, size_t workspace_bytes, int64_t M, int64_t N, int io_dtype, int w_dtype,
-             void* stream_v) {
+             void* stream_v, const b200norm_peers* peers = nullptr, uint64_t seq = 0) {
   if (int rc = check_common(M, N, io_dtype, w_dtype)) return rc;
+  if (peers != nullptr) {
+    if (int rc = check_peers(peers, seq, (op == kLN) ? 2 : 1, N, row_shards)) return rc;
+  }
   if (row_shards < 1 || M % row_shards != 0)
     return fail(B200NORM_ERR_ARG, "row_shards=%d must be >= 1 and divide M=%lld", row_shards, (long long)M);
   if (M > 0 && (!x || !dy || !dx || !rstd || (op == kLN && !mean)))
     return fail(B200NORM_ERR_ARG, "null x / dy / dx / mean / rstd");
   if (xs < N || dys < N || dxs < N) return fail(B200NORM_ERR_ARG, "row stride smaller than N");
   if (op == kRMS) db = nullptr;
-  const bool want_params = dw != nullptr || db != nullptr || group_sums != nullptr;
+  const bool want_params = dw != nullptr || db != nullptr || group_sums != nullptr || peers != nullptr;
   if (M == 0 && !want_params) return B200NORM_OK;
   DeviceState* dev;
   if (int rc = device_state(&dev)) return rc;
@@ -241,8 +276,8 @@ int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, con
     const size_t need = partial_bytes(P, N) * slots;
     if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))
       return fail(B200NORM_ERR_ARG, "workspace needs %zu bytes, 256-byte aligned (got %zu)", need, workspace_bytes);
-    const bool want_dw = dw != nullptr || group_sums != nullptr;
-    const bool want_db = op == kLN && (db != nullptr || group_sums != nullptr);
+    const bool want_dw = dw != nullptr || group_sums != nullptr || peers != nullptr;
+    const bool want_db = op == kLN && (db != nullptr || group_sums != nullptr || peers != nullptr);
     if (want_dw) p.dw_part = static_cast<float*>(workspace);
     if (want_db) p.db_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + partial_bytes(P, N));
   }
@@ -264,6 +299,16 @@ int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, con
     }
   }
   if (!want_params) return B200NORM_OK;
+
+  if (peers != nullptr) {  // column reduce fused with the push to every rank's inbox
+    ColReducePushParams c;
+    c.part[0] = p.dw_part; c.part[1] = p.db_part;
+    c.peers = peer_targets(peers);
+    c.seq = seq;
+    c.per_shard = plan.ctas_per_shard; c.row_shards = row_shards; c.slots = slots; c.N = static_cast<int>(N);
+    return launch(reinterpret_cast<const void*>(&colreduce_push_kernel),
+                  dim3(static_cast<unsigned>((N + 31) / 32), slots), dim3(32, 16), 0, &c, stream);
+  }
 
   ColReduceParams c;
   c.part[0] = p.dw_part; c.part[1] = p.db_part;
@@ -462,6 +507,46 @@ int b200norm_finalize_dwdb(const float* group_sums, int groups, int slots, void*
   p.groups = groups; p.slots = slots; p.N = static_cast<int>(N); p.w_dtype = w_dtype;
   return launch(reinterpret_cast<const void*>(&finalize_kernel), dim3(static_cast<unsigned>((N + 255) / 256), slots),
                 dim3(256), 0, &p, static_cast<cudaStream_t>(stream));
+}
+
+int b200norm_ln_bwd_push(const void* x, int64_t x_row_stride, const void* dy, int64_t dy_row_stride, const void* w,
+                         const float* mean, const float* rstd, void* dx, int64_t dx_row_stride, int row_shards,
+                         void* workspace, size_t workspace_bytes, int64_t M, int64_t N, int io_dtype, int w_dtype,
+                         const b200norm_peers* peers, uint64_t seq, void* stream) {
+  if (peers == nullptr) return fail(B200NORM_ERR_ARG, "null peers");
+  return bwd_impl(kLN, x, x_row_stride, dy, dy_row_stride, w, mean, rstd, dx, dx_row_stride, nullptr, nullptr,
+                  nullptr, row_shards, workspace, workspace_bytes, M, N, io_dtype, w_dtype, stream, peers, seq);
+}
+
+int b200norm_rms_bwd_push(const void* x, int64_t x_row_stride, const void* dy, int64_t dy_row_stride, const void* w,
+                          const float* rstd, void* dx, int64_t dx_row_stride, int row_shards, void* workspace,
+                          size_t workspace_bytes, int64_t M, int64_t N, int io_dtype, int w_dtype,
+                          const b200norm_peers* peers, uint64_t seq, void* stream) {
+  if (peers == nullptr) return fail(B200NORM_ERR_ARG, "null peers");
+  return bwd_impl(kRMS, x, x_row_stride, dy, dy_row_stride, w, nullptr, rstd, dx, dx_row_stride, nullptr, nullptr,
+                  nullptr, row_shards, workspace, workspace_bytes, M, N, io_dtype, w_dtype, stream, peers, seq);
+}
+
+int b200norm_finalize_pushed(const b200norm_peers* peers, uint64_t seq, int slots, void* dw, void* db, int64_t N,
+                             int w_dtype, void* stream) {
+  if (peers == nullptr || (slots != 1 && slots != 2) || N < 1 || !valid_dtype(w_dtype))
+    return fail(B200NORM_ERR_ARG, "bad finalize_pushed arguments (slots=%d N=%lld)", slots, (long long)N);
+  if (int rc = check_peers(peers, seq, slots, N, 0)) return rc;
+  DeviceState* dev;
+  if (int rc = device_state(&dev)) return rc;
+  FinalizePushedParams p;
+  p.inbox = static_cast<const float*>(peers->inbox[peers->rank]);
+  p.flags = static_cast<const unsigned long long*>(peers->flags[peers->rank]);
+  p.out[0] = dw;
+  p.out[1] = (slots == 2) ? db : nullptr;
+  p.status = dev->status_dev;
+  p.seq = seq;
+  p.world = peers->world; p.depth = peers->depth; p.total_shards = peers->total_shards;
+  p.slot_floats = peers->inbox_bytes / sizeof(float) / peers->depth;
+  p.slots = slots; p.N = static_cast<int>(N); p.w_dtype = w_dtype;
+  return launch(reinterpret_cast<const void*>(&finalize_pushed_kernel),
+                dim3(static_cast<unsigned>((N + 255) / 256), slots), dim3(256), 0, &p,
+                static_cast<cudaStream_t>(stream));
 }
 
 int b200norm_rms_bwd_static(const void* x, int64_t x_row_stride, const void* dy, int64_t dy_row_stride,
