@@ -2,7 +2,8 @@
 CUDA kernels behind TritonHub's module and autograd.Function interface."""
 from .functional import (_layernorm_bwd, _layernorm_fwd, _rmsnorm_bwd, _rmsnorm_fwd, finalize_dwdb, layernorm,
                          rmsnorm)
+from .hostio import HostPipeline
 from .modules import LayerNorm, RMSNorm
 
-__all__ = ['LayerNorm', 'RMSNorm', 'layernorm', 'rmsnorm', 'finalize_dwdb']
+__all__ = ['LayerNorm', 'RMSNorm', 'layernorm', 'rmsnorm', 'finalize_dwdb', 'HostPipeline']
 __version__ = '0.1.0'

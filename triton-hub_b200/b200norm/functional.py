@@ -12,6 +12,8 @@ fallback path.
 """
 from __future__ import annotations
 
+import contextlib
+
 import torch
 
 from . import _lib
@@ -22,6 +24,32 @@ _DTYPE_CODE = {
     torch.bfloat16: _lib.BF16,
     torch.float64: _lib.F64,
 }
+
+
+_NULL_CTX = contextlib.nullcontext()
+_WS_BYTES = {}  # (device, M, N, dtype code, row_shards) -> workspace bytes; the answer never changes
+
+try:  # the raw cudaStream_t of the current stream without building a Stream object
+    _raw_stream = torch._C._cuda_getCurrentRawStream
+except AttributeError:  # pragma: no cover
+    def _raw_stream(index):
+        return torch.cuda.current_stream(index).cuda_stream
+
+
+def _on_device(index: int):
+    """Context that makes `index` the current device; free when it already is (the usual case)."""
+    return _NULL_CTX if torch.cuda.current_device() == index else torch.cuda.device(index)
+
+
+def _workspace_bytes(lib, index, M, N, code, row_shards):
+    key = (index, M, N, code, row_shards)
+    n = _WS_BYTES.get(key)
+    if n is None:
+        n = lib.b200norm_bwd_workspace_bytes(M, N, code, row_shards)
+        if n == 0:
+            _lib.check(_lib.ERR_ARG)
+        _WS_BYTES[key] = n
+    return n
 
 
 def _code(t: torch.Tensor, what: str) -> int:
@@ -91,11 +119,11 @@ def _layernorm_fwd(x, weight, bias, eps):
     rstd = torch.empty((M,), dtype=torch.float32, device=x.device)
     _check_dim(x, N)
     lib = _lib.load()
-    with torch.cuda.device(x.device.index):
+    with _on_device(x.device.index):
         _lib.check(lib.b200norm_ln_fwd(
             x.data_ptr(), _row_stride(x), _ptr(weight), _ptr(bias), out.data_ptr(), N,
             mean.data_ptr(), rstd.data_ptr(), M, N, float(eps), _code(x, "input"), wcode,
-            torch.cuda.current_stream().cuda_stream))
+            _raw_stream(x.device.index)))
     return out.reshape(*batch_shape, N), mean, rstd
 
 
@@ -110,10 +138,10 @@ def _rmsnorm_fwd(x, weight, eps):
     rstd = torch.empty((M,), dtype=torch.float32, device=x.device)
     _check_dim(x, N)
     lib = _lib.load()
-    with torch.cuda.device(x.device.index):
+    with _on_device(x.device.index):
         _lib.check(lib.b200norm_rms_fwd(
             x.data_ptr(), _row_stride(x), _ptr(weight), out.data_ptr(), N, rstd.data_ptr(), M, N,
-            float(eps), _code(x, "input"), wcode, torch.cuda.current_stream().cuda_stream))
+            float(eps), _code(x, "input"), wcode, _raw_stream(x.device.index)))
     return out.reshape(*batch_shape, N), rstd
 
 
@@ -135,14 +163,12 @@ def _bwd_common(op, x, dout, weight, bias, mean, rstd, row_shards, want_group_su
     gs = (torch.empty((row_shards, slots, N), dtype=torch.float32, device=x.device)
           if want_group_sums else None)
     lib = _lib.load()
-    with torch.cuda.device(x.device.index):
+    with _on_device(x.device.index):
         ws, ws_bytes = None, 0
         if dw is not None or db is not None or gs is not None or push is not None:
-            ws_bytes = lib.b200norm_bwd_workspace_bytes(M, N, _code(x, "input"), row_shards)
-            if ws_bytes == 0:
-                _lib.check(_lib.ERR_ARG)
+            ws_bytes = _workspace_bytes(lib, x.device.index, M, N, _code(x, "input"), row_shards)
             ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=x.device)
-        stream = torch.cuda.current_stream().cuda_stream
+        stream = _raw_stream(x.device.index)
         if push is not None:  # (Peers struct, sequence number): shard sums go to every rank's inbox
             peers, seq = push
             if op == "ln":
@@ -198,11 +224,10 @@ def finalize_dwdb(group_sums: torch.Tensor, w_dtype: torch.dtype):
     outs = [torch.empty((N,), dtype=w_dtype, device=group_sums.device) for _ in range(slots)]
     code = _DTYPE_CODE[w_dtype]
     lib = _lib.load()
-    with torch.cuda.device(group_sums.device.index):
+    with _on_device(group_sums.device.index):
         _lib.check(lib.b200norm_finalize_dwdb(
             group_sums.data_ptr(), groups, slots, outs[0].data_ptr(),
-            outs[1].data_ptr() if slots == 2 else None, N, code,
-            torch.cuda.current_stream().cuda_stream))
+            outs[1].data_ptr() if slots == 2 else None, N, code, _raw_stream(group_sums.device.index)))
     return tuple(outs)
 
 
@@ -211,10 +236,11 @@ def finalize_pushed(peers, seq, slots, N, w_dtype, device):
     (b200norm_finalize_pushed; the wait happens on the GPU, bounded)."""
     outs = [torch.empty((N,), dtype=w_dtype, device=device) for _ in range(slots)]
     lib = _lib.load()
-    with torch.cuda.device(device):
+    index = torch.device(device).index
+    with _on_device(index):
         _lib.check(lib.b200norm_finalize_pushed(
             peers, seq, slots, outs[0].data_ptr(), outs[1].data_ptr() if slots == 2 else None, N,
-            _DTYPE_CODE[w_dtype], torch.cuda.current_stream().cuda_stream))
+            _DTYPE_CODE[w_dtype], _raw_stream(index)))
     return tuple(outs)
 
 

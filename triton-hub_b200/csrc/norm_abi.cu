@@ -6,6 +6,7 @@
 #include <algorithm>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -114,9 +115,30 @@ const PacketKernel* pick(const PacketKernel* tab, int n, int64_t V) {
   return nullptr;
 }
 
-int launch(const void* fn, dim3 grid, dim3 block, size_t smem, void* params, cudaStream_t stream) {
+// `pdl`: launch with programmatic stream serialization (the kernel calls grid_dependency_sync()
+// before its first global access); the any-alignment kernels do not and are launched plainly.
+int launch(const void* fn, dim3 grid, dim3 block, size_t smem, void* params, cudaStream_t stream, bool pdl = true) {
   void* args[1] = {params};
-  cudaError_t e = cudaLaunchKernel(fn, grid, block, args, smem, stream);
+  cudaError_t e;
+  static const bool pdl_enabled = []() {  // B200NORM_PDL=0 turns programmatic dependent launch off (A/B timing)
+    const char* v = std::getenv("B200NORM_PDL");
+    return !(v != nullptr && v[0] == '0');
+  }();
+  if (pdl && pdl_enabled) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelExC(&cfg, fn, args);
+  } else {
+    e = cudaLaunchKernel(fn, grid, block, args, smem, stream);
+  }
   if (e != cudaSuccess) return fail(B200NORM_ERR_CUDA, "kernel launch: %s", cudaGetErrorString(e));
   return B200NORM_OK;
 }
@@ -165,7 +187,7 @@ int fwd_impl(int op, const void* x, int64_t xs, const void* w, const void* b, vo
   int occ;
   if (int rc = occupancy(*dev, k->fwd_any[op], 256, 0, &occ)) return rc;
   const int grid = static_cast<int>(std::min<int64_t>(M, (int64_t)dev->sm_count * occ));
-  return launch(k->fwd_any[op], dim3(grid), dim3(256), 0, &p, static_cast<cudaStream_t>(stream));
+  return launch(k->fwd_any[op], dim3(grid), dim3(256), 0, &p, static_cast<cudaStream_t>(stream), false);
 }
 
 // How a backward call is laid out: which kernel, how many partial rows.
@@ -291,11 +313,11 @@ int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, con
       int occ;
       if (int rc = occupancy(*dev, k->bwd_dx_any[op], 256, 0, &occ)) return rc;
       const int grid = static_cast<int>(std::min<int64_t>(M, (int64_t)dev->sm_count * occ));
-      if (int rc = launch(k->bwd_dx_any[op], dim3(grid), dim3(256), 0, &p, stream)) return rc;
+      if (int rc = launch(k->bwd_dx_any[op], dim3(grid), dim3(256), 0, &p, stream, false)) return rc;
     }
     if (want_params) {
       const dim3 grid(static_cast<unsigned>((N + 255) / 256), static_cast<unsigned>(P));
-      if (int rc = launch(k->bwd_dwdb_any[op], grid, dim3(256), 0, &p, stream)) return rc;
+      if (int rc = launch(k->bwd_dwdb_any[op], grid, dim3(256), 0, &p, stream, false)) return rc;
     }
   }
   if (!want_params) return B200NORM_OK;
@@ -404,11 +426,11 @@ int rms_bwd_static_impl(const void* x, int64_t xs, const void* dy, int64_t dys, 
       int occ;
       if (int rc = occupancy(st->dev, k->bwd_dx_any[kRMS], 256, 0, &occ)) return rc;
       const int grid = static_cast<int>(std::min<int64_t>(M, (int64_t)st->dev.sm_count * occ));
-      if (int rc = launch(k->bwd_dx_any[kRMS], dim3(grid), dim3(256), 0, &p, stream)) return rc;
+      if (int rc = launch(k->bwd_dx_any[kRMS], dim3(grid), dim3(256), 0, &p, stream, false)) return rc;
     }
     if (dw != nullptr) {
       const dim3 grid(static_cast<unsigned>((N + 255) / 256), static_cast<unsigned>(P));
-      if (int rc = launch(k->bwd_dwdb_any[kRMS], grid, dim3(256), 0, &p, stream)) return rc;
+      if (int rc = launch(k->bwd_dwdb_any[kRMS], grid, dim3(256), 0, &p, stream, false)) return rc;
     }
   }
   if (dw == nullptr) return B200NORM_OK;

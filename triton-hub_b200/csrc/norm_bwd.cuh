@@ -99,6 +99,8 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
     cta_abort = 0;
     mbar_init_fence();
   }
+  grid_dependency_sync();  // nothing above reads global memory
+  trigger_dependents();
   for (int c = threadIdx.x; c < p.N; c += WARPS_M * TPR)
     w_s[c] = (p.w != nullptr) ? load_param(p.w, p.w_dtype, c) : 1.f;
   __syncthreads();

@@ -27,6 +27,8 @@ __global__ void __launch_bounds__(512) colreduce_kernel(const ColReduceParams p)
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int col = blockIdx.x * 32 + tx;
   const int slot = blockIdx.y;
+  grid_dependency_sync();
+  trigger_dependents();
   const float* part = p.part[slot];
   const bool live = col < p.N && part != nullptr;
   float total = 0.f;
@@ -63,6 +65,8 @@ struct FinalizeParams {
 __global__ void __launch_bounds__(256) finalize_kernel(const FinalizeParams p) {
   const int col = blockIdx.x * 256 + threadIdx.x;
   const int slot = blockIdx.y;
+  grid_dependency_sync();
+  trigger_dependents();
   if (col >= p.N || p.out[slot] == nullptr) return;
   float total = 0.f;
   for (int g = 0; g < p.groups; ++g) total += p.group_sums[((size_t)g * p.slots + slot) * p.N + col];

@@ -168,6 +168,18 @@ __device__ __forceinline__ void st_stream(uint4* p, const uint4& v) {
 }
 
 // ---------------------------------------------------------------------------------------
+// Programmatic dependent launch.  The kernels are launched with the "programmatic stream
+// serialization" attribute: a kernel may be scheduled while its predecessor in the stream is
+// still draining, and must call grid_dependency_sync() before it touches global memory; that
+// returns once the predecessor has completed and its writes are visible.  Calling
+// trigger_dependents() early lets the successor's CTAs take SM slots as this grid's CTAs retire,
+// which hides launch latency and the ramp-up of the next kernel behind this kernel's tail.
+// After a predecessor that never triggers (any ordinary kernel) the launch behaves as usual.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void grid_dependency_sync() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void trigger_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------------
 // Reductions.
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {

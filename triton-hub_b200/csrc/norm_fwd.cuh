@@ -75,6 +75,10 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
       mbar_init_fence();
     }
     __syncthreads();
+  }
+  grid_dependency_sync();  // nothing above reads global memory
+  trigger_dependents();
+  if (STAGES > 0) {
     if (t == 0) {
 #pragma unroll
       for (int s = 0; s < STAGES; ++s) {

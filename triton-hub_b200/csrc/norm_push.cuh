@@ -58,6 +58,8 @@ __global__ void __launch_bounds__(512) colreduce_push_kernel(const ColReducePush
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int col = blockIdx.x * 32 + tx;
   const int slot = blockIdx.y;
+  grid_dependency_sync();
+  trigger_dependents();
   const float* part = p.part[slot];
   const bool live = col < p.N && part != nullptr;
   const int buf = static_cast<int>(p.seq % static_cast<unsigned long long>(p.peers.depth));
@@ -110,6 +112,8 @@ struct FinalizePushedParams {
 // on with whatever the inbox holds, so the stream never hangs.
 __global__ void __launch_bounds__(256) finalize_pushed_kernel(const FinalizePushedParams p) {
   const int buf = static_cast<int>(p.seq % static_cast<unsigned long long>(p.depth));
+  grid_dependency_sync();
+  trigger_dependents();
   if (threadIdx.x < p.world) {
     const unsigned long long* f = p.flags + (size_t)buf * p.world + threadIdx.x;
     if (ld_acquire_sys(f) < p.seq) {
