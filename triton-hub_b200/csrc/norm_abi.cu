@@ -67,8 +67,9 @@ int device_state(DeviceState** out) {
   return B200NORM_OK;
 }
 
-// Resident CTAs per SM of `fn` at this block size and dynamic shared memory; cached.
-int occupancy(DeviceState& s, const void* fn, int threads, size_t smem, int* out) {
+// Resident CTAs per SM of `fn` at this block size and dynamic shared memory (cluster == 1), or
+// resident clusters on the whole device (cluster > 1); cached.
+int occupancy(DeviceState& s, const void* fn, int threads, size_t smem, int* out, int cluster = 1) {
   const unsigned long long key =
       (reinterpret_cast<unsigned long long>(fn) * 0x9E3779B97F4A7C15ull) ^ (unsigned long long)smem;
   std::lock_guard<std::mutex> lock(s.mu);
@@ -84,7 +85,22 @@ int occupancy(DeviceState& s, const void* fn, int threads, size_t smem, int* out
       return fail(B200NORM_ERR_CUDA, "cudaFuncSetAttribute(%zu B): %s", smem, cudaGetErrorString(e));
   }
   int n = 0;
-  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, fn, threads, smem);
+  if (cluster > 1) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(cluster * s.sm_count));
+    cfg.blockDim = dim3(static_cast<unsigned>(threads));
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(cluster);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaOccupancyMaxActiveClusters(&n, fn, &cfg);
+  } else {
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, fn, threads, smem);
+  }
   if (e != cudaSuccess) return fail(B200NORM_ERR_CUDA, "occupancy query: %s", cudaGetErrorString(e));
   if (n < 1) return fail(B200NORM_ERR_CUDA, "kernel does not fit on an SM (%d threads, %zu B smem)", threads, smem);
   s.occupancy.emplace(key, n);
@@ -111,30 +127,42 @@ bool aligned16(const void* p, int64_t stride_elems, int es) {
 // First table entry whose capacity covers a row of V packets, or null.
 const PacketKernel* pick(const PacketKernel* tab, int n, int64_t V) {
   for (int i = 0; i < n; ++i)
-    if (tab[i].capacity() >= V) return &tab[i];
+    if (tab[i].capacity() >= V && V % tab[i].cluster == 0) return &tab[i];
   return nullptr;
 }
 
 // `pdl`: launch with programmatic stream serialization (the kernel calls grid_dependency_sync()
 // before its first global access); the any-alignment kernels do not and are launched plainly.
-int launch(const void* fn, dim3 grid, dim3 block, size_t smem, void* params, cudaStream_t stream, bool pdl = true) {
+int launch(const void* fn, dim3 grid, dim3 block, size_t smem, void* params, cudaStream_t stream, bool pdl = true,
+           int cluster = 1) {
   void* args[1] = {params};
   cudaError_t e;
   static const bool pdl_enabled = []() {  // B200NORM_PDL=0 turns programmatic dependent launch off (A/B timing)
     const char* v = std::getenv("B200NORM_PDL");
     return !(v != nullptr && v[0] == '0');
   }();
-  if (pdl && pdl_enabled) {
+  if ((pdl && pdl_enabled) || cluster > 1) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (pdl && pdl_enabled) {
+      attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+      ++n_attr;
+    }
+    if (cluster > 1) {
+      attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+      attr[n_attr].val.clusterDim.x = static_cast<unsigned>(cluster);
+      attr[n_attr].val.clusterDim.y = 1;
+      attr[n_attr].val.clusterDim.z = 1;
+      ++n_attr;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = n_attr;
     e = cudaLaunchKernelExC(&cfg, fn, args);
   } else {
     e = cudaLaunchKernel(fn, grid, block, args, smem, stream);
@@ -211,13 +239,16 @@ int plan_bwd(DeviceState& dev, const DTypeKernels* k, int op, int64_t rows_per_s
     return B200NORM_OK;
   }
   const PacketKernel* pk = plan->pk;
-  // fp32 weights / cross-group sums, padded to 128 bytes, then the x+dy row slots
-  plan->smem = ((static_cast<size_t>(pk->warps_m) * N * sizeof(float) + 127) & ~static_cast<size_t>(127)) +
-               static_cast<size_t>(pk->warps_m) * pk->stages * 2 * (N * es);
-  int occ;
-  if (int rc = occupancy(dev, pk->fn, pk->threads(), plan->smem, &occ)) return rc;
+  // per CTA: fp32 weights / cross-group sums, padded to 128 bytes, then the x+dy row slots; a CTA
+  // of a pair holds half of each
+  const int64_t Nl = N / pk->cluster;
+  plan->smem = ((static_cast<size_t>(pk->warps_m) * Nl * sizeof(float) + 127) & ~static_cast<size_t>(127)) +
+               static_cast<size_t>(pk->warps_m) * pk->stages * 2 * (Nl * es);
+  int occ;  // resident CTAs per SM, or resident clusters per device
+  if (int rc = occupancy(dev, pk->fn, pk->threads(), plan->smem, &occ, pk->cluster)) return rc;
+  const int64_t resident = (pk->cluster > 1) ? occ : (int64_t)dev.sm_count * occ;
   const int64_t want = std::max<int64_t>(1, (rows_per_shard + pk->warps_m - 1) / pk->warps_m);
-  plan->ctas_per_shard = static_cast<int>(std::min<int64_t>(want, (int64_t)dev.sm_count * occ));
+  plan->ctas_per_shard = static_cast<int>(std::min<int64_t>(want, resident));  // units: CTAs or CTA pairs
   return B200NORM_OK;
 }
 
@@ -305,8 +336,8 @@ int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, con
   }
 
   if (plan.pk != nullptr) {
-    if (int rc = launch(plan.pk->fn, dim3(static_cast<unsigned>(P)), dim3(plan.pk->threads()), plan.smem, &p,
-                        stream))
+    if (int rc = launch(plan.pk->fn, dim3(static_cast<unsigned>(P * plan.pk->cluster)), dim3(plan.pk->threads()),
+                        plan.smem, &p, stream, true, plan.pk->cluster))
       return rc;
   } else {
     if (M > 0) {
@@ -419,7 +450,8 @@ int rms_bwd_static_impl(const void* x, int64_t xs, const void* dy, int64_t dys, 
   p.status = st->dev.status_dev;
 
   if (plan.pk != nullptr) {
-    if (int rc = launch(plan.pk->fn, dim3(static_cast<unsigned>(P)), dim3(plan.pk->threads()), plan.smem, &p, stream))
+    if (int rc = launch(plan.pk->fn, dim3(static_cast<unsigned>(P * plan.pk->cluster)), dim3(plan.pk->threads()),
+                        plan.smem, &p, stream, true, plan.pk->cluster))
       return rc;
   } else {
     if (M > 0) {

@@ -52,12 +52,21 @@ struct BwdParams {
 // KEEP: xhat and w*dy of the current row stay in fp32 registers between the two passes
 // instead of being recomputed from the packed row (fewer instructions, more registers).
 // MINB is the number of CTAs per SM the register allocation must leave room for.
-template <typename T, int LDGS, int WARPS_M, int WARPS_N, bool PREFETCH, int STAGES, bool KEEP, int MINB, bool RMS>
+//
+// CL == 2: rows wider than one CTA's registers can carry (32 - 64 KB).  The kernel is launched
+// in clusters of two CTAs; each CTA of a pair stages, reduces and writes one half of the columns
+// of every row the pair owns, and the two halves of the row sums are swapped through distributed
+// shared memory (one remote store + one cluster barrier per row).  Both CTAs add the halves in
+// rank order, so they hold identical sums.  A "unit" below is the CTA (CL == 1) or the pair.
+template <typename T, int LDGS, int WARPS_M, int WARPS_N, bool PREFETCH, int STAGES, bool KEEP, int MINB, int CL,
+          bool RMS>
 __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(const BwdParams p) {
+  static_assert(CL == 1 || (CL == 2 && WARPS_M == 1 && STAGES > 0), "cluster split: one row group, staged rows");
   constexpr int VEC = Pack16<T>::kElems;
   constexpr int TPR = WARPS_N * 32;
   constexpr int NV = RMS ? 1 : 2;
   constexpr int NBAR = STAGES > 0 ? WARPS_M * STAGES : 1;
+  __shared__ float pair_sums[2][NV];  // CL == 2: the partner's row sums, double-buffered
   // w as fp32 (N), later the (WARPS_M, N) sums; then, 128-byte aligned, the row slots
   extern __shared__ __align__(128) unsigned char dyn_smem[];
   __shared__ float red_smem[WARPS_M][2 * NV * WARPS_N];
@@ -69,8 +78,14 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
   const int t = warp_n * 32 + lane;
   int phase = 0;
 
-  const int shard = blockIdx.x / p.ctas_per_shard;
-  const int cta_in_shard = blockIdx.x - shard * p.ctas_per_shard;
+  const uint32_t cr = (CL > 1) ? cluster_cta_rank() : 0u;
+  const int unit = (CL > 1) ? static_cast<int>(blockIdx.x) / CL : static_cast<int>(blockIdx.x);
+  const int Vl = p.V / CL;                       // packets of each row this CTA handles ...
+  const int v0 = static_cast<int>(cr) * Vl;      // ... starting at this one
+  const int Nl = Vl * VEC;                       // the same in elements
+  int pair_buf = 0;
+  const int shard = unit / p.ctas_per_shard;
+  const int cta_in_shard = unit - shard * p.ctas_per_shard;
   const int64_t row_begin = (int64_t)shard * p.rows_per_shard;
   const int64_t row_end = min(row_begin + p.rows_per_shard, p.M);
   const int64_t step = (int64_t)p.ctas_per_shard * WARPS_M;
@@ -82,16 +97,16 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
   const float inv_n = 1.f / static_cast<float>(p.N);
 
   float* w_s = reinterpret_cast<float*>(dyn_smem);
-  const uint32_t row_bytes = static_cast<uint32_t>(p.V) * 16u;
-  const size_t param_bytes = ((size_t)WARPS_M * p.N * sizeof(float) + 127) & ~(size_t)127;
+  const uint32_t row_bytes = static_cast<uint32_t>(Vl) * 16u;
+  const size_t param_bytes = ((size_t)WARPS_M * Nl * sizeof(float) + 127) & ~(size_t)127;
   unsigned char* slots = dyn_smem + param_bytes + (size_t)warp_m * STAGES * 2 * row_bytes;
   uint64_t* bars = full_bar + (STAGES > 0 ? warp_m * STAGES : 0);
 
   auto fill = [&](int s, int64_t r) {  // leader only: x row then dy row into slot s
     unsigned char* dst = slots + (size_t)s * 2 * row_bytes;
     mbar_expect_tx(&bars[s], 2 * row_bytes);
-    bulk_load(dst, xb + r * p.x_stride, row_bytes, &bars[s]);
-    bulk_load(dst + row_bytes, gb + r * p.dy_stride, row_bytes, &bars[s]);
+    bulk_load(dst, xb + r * p.x_stride + (size_t)v0 * VEC, row_bytes, &bars[s]);
+    bulk_load(dst + row_bytes, gb + r * p.dy_stride + (size_t)v0 * VEC, row_bytes, &bars[s]);
   };
 
   if (STAGES > 0 && threadIdx.x == 0) {
@@ -101,9 +116,10 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
   }
   grid_dependency_sync();  // nothing above reads global memory
   trigger_dependents();
-  for (int c = threadIdx.x; c < p.N; c += WARPS_M * TPR)
-    w_s[c] = (p.w != nullptr) ? load_param(p.w, p.w_dtype, c) : 1.f;
+  for (int c = threadIdx.x; c < Nl; c += WARPS_M * TPR)
+    w_s[c] = (p.w != nullptr) ? load_param(p.w, p.w_dtype, (int64_t)v0 * VEC + c) : 1.f;
   __syncthreads();
+  if (CL > 1) cluster_sync_all();  // the partner CTA is running: its shared memory may be written
   if (STAGES > 0 && t == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) {
@@ -127,7 +143,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
       const int v = j * TPR + t;
       xo[j] = make_uint4(0, 0, 0, 0);
       go[j] = make_uint4(0, 0, 0, 0);
-      if (v < p.V) {
+      if (v < Vl) {
         xo[j] = ld_stream(xrow + v);
         go[j] = ld_stream(grow + v);
       }
@@ -163,7 +179,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
         const int v = j * TPR + t;
         xv[j] = make_uint4(0, 0, 0, 0);
         gv[j] = make_uint4(0, 0, 0, 0);
-        if (v < p.V) {
+        if (v < Vl) {
           xv[j] = ld_shared16(sx + v);
           gv[j] = ld_shared16(sg + v);
         }
@@ -179,7 +195,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
 #pragma unroll
     for (int j = 0; j < LDGS; ++j) {
       const int v = j * TPR + t;
-      if (v < p.V) {
+      if (v < Vl) {
         float xf[VEC], gf[VEC];
         Pack16<T>::unpack(xv[j], xf);
         Pack16<T>::unpack(gv[j], gf);
@@ -199,6 +215,20 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
       }
     }
     group_sum<WARPS_N, NV>(s, red_smem[warp_m], phase, warp_m, warp_n, lane);
+    if (CL > 1) {
+      // Swap this half's sums with the partner's and add them in rank order.
+      if (threadIdx.x == 0) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) st_cluster_f32(cluster_map(smem_addr(&pair_sums[pair_buf][i]), cr ^ 1u), s[i]);
+      }
+      cluster_sync_all();
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const float other = pair_sums[pair_buf][i];
+        s[i] = (cr == 0) ? s[i] + other : other + s[i];
+      }
+      pair_buf ^= 1;
+    }
     if (STAGES > 0) {
       // Every thread of the group holds its packets in registers: the slot can be refilled.
       if (t == 0) {
@@ -213,26 +243,27 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
     const float c1 = s[0] * inv_n;
     const float c2 = RMS ? 0.f : s[NV - 1] * inv_n;
 
-    // Pass 2: dx = (wdy - (xhat*c1 + c2)) * rstd (layernorm.py:139).
-    uint4* dxrow = reinterpret_cast<uint4*>(dxb + row * p.dx_stride);
+    // Pass 2: dx = (wdy - (xhat*c1 + c2)) * rstd (layernorm.py:139), with the row's scalars folded
+    // so that each element costs two FMAs:
+    //   kept   : dx = xhat * (-c1*rstd) + (wdy * rstd + (-c2*rstd))
+    //   packed : dx = (w*rstd) * dy + (x * (-c1*rstd^2) + (c1*rstd^2*mean - c2*rstd))
+    uint4* dxrow = reinterpret_cast<uint4*>(dxb + row * p.dx_stride) + v0;
+    const float k1 = -c1 * rs, k2 = -c2 * rs;
+    const float kb = k1 * rs, kc = -kb * mu + k2;
 #pragma unroll
     for (int j = 0; j < LDGS; ++j) {
       const int v = j * TPR + t;
-      if (v < p.V) {
+      if (v < Vl) {
         float o[VEC];
         if (KEEP) {
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) o[e] = (wdy_k[j][e] - (xh_k[j][e] * c1 + c2)) * rs;
+          for (int e = 0; e < VEC; ++e) o[e] = fmaf(xh_k[j][e], k1, fmaf(wdy_k[j][e], rs, k2));
         } else {
           float xf[VEC], gf[VEC];
           Pack16<T>::unpack(xv[j], xf);
           Pack16<T>::unpack(gv[j], gf);
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) {
-            const float xh = (xf[e] - mu) * rs;
-            const float wdy = w_s[v * VEC + e] * gf[e];
-            o[e] = (wdy - (xh * c1 + c2)) * rs;
-          }
+          for (int e = 0; e < VEC; ++e) o[e] = fmaf(w_s[v * VEC + e] * rs, gf[e], fmaf(xf[e], kb, kc));
         }
         st_stream(dxrow + v, Pack16<T>::pack(o));
       }
@@ -257,7 +288,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
     if (t == 0 && cta_abort) drain_ring<STAGES>(bars, first < row_end ? (row_end - first + step - 1) / step : 0);
   }
 
-  // One partial row per CTA: add the row groups in order, then row group 0 stores.
+  // One partial row per unit: add the row groups in order, then row group 0 stores.
   if (WARPS_M > 1) {
     float* acc = reinterpret_cast<float*>(dyn_smem);  // (WARPS_M, N); the weights are no longer needed
 #pragma unroll
@@ -266,10 +297,10 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
 #pragma unroll
       for (int j = 0; j < LDGS; ++j) {
         const int v = j * TPR + t;
-        if (v < p.V) {
+        if (v < Vl) {
 #pragma unroll
           for (int e = 0; e < VEC; ++e)
-            acc[(size_t)warp_m * p.N + v * VEC + e] = (pass == 0) ? dw[j][e] : db[j][e];
+            acc[(size_t)warp_m * Nl + v * VEC + e] = (pass == 0) ? dw[j][e] : db[j][e];
         }
       }
       __syncthreads();
@@ -277,11 +308,11 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
 #pragma unroll
         for (int j = 0; j < LDGS; ++j) {
           const int v = j * TPR + t;
-          if (v < p.V) {
+          if (v < Vl) {
 #pragma unroll
             for (int e = 0; e < VEC; ++e) {
               float a = 0.f;
-              for (int m = 0; m < WARPS_M; ++m) a += acc[(size_t)m * p.N + v * VEC + e];
+              for (int m = 0; m < WARPS_M; ++m) a += acc[(size_t)m * Nl + v * VEC + e];
               if (pass == 0) dw[j][e] = a;
               else db[j][e] = a;
             }
@@ -294,8 +325,8 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
 #pragma unroll
     for (int j = 0; j < LDGS; ++j) {
       const int v = j * TPR + t;
-      if (v < p.V) {
-        const size_t o = (size_t)blockIdx.x * p.N + (size_t)v * VEC;
+      if (v < Vl) {
+        const size_t o = (size_t)unit * p.N + (size_t)(v0 + v) * VEC;
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
           if (p.dw_part != nullptr) p.dw_part[o + e] = dw[j][e];

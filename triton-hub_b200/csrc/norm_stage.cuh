@@ -87,6 +87,31 @@ __device__ __forceinline__ void drain_ring(uint64_t* bars, int64_t count) {
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// Thread-block clusters: a row too wide for one CTA's registers is split over a pair of CTAs on
+// neighbouring SMs, which exchange their partial row sums through distributed shared memory.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of `local` (a shared-memory address of this CTA) in CTA `cta` of the cluster.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local, uint32_t cta) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(cta));
+  return remote;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+// Hardware barrier over every thread of the cluster (release / acquire: remote shared-memory
+// stores made before it are visible after it).  Like __syncthreads, it relies on the hardware
+// co-scheduling all CTAs of a cluster; it is not a software spin.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ uint4 ld_shared16(const void* p) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"

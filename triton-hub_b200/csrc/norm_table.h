@@ -10,9 +10,10 @@ namespace b200norm {
 struct PacketKernel {
   int ldgs, warps_m, warps_n;
   int stages;          // shared-memory slots per row group filled by bulk copies (0: none)
+  int cluster;         // CTAs that share one row (1, or 2: column halves on a CTA pair)
   bool packet_params;  // re-reads weight / bias per row as 16-byte packets: they must be aligned
   const void* fn;
-  int capacity() const { return ldgs * 32 * warps_n; }  // packets per row it can hold
+  int capacity() const { return ldgs * 32 * warps_n * cluster; }  // packets per row it can hold
   int threads() const { return 32 * warps_m * warps_n; }
 };
 
