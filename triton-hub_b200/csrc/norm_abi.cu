@@ -205,12 +205,15 @@ int fwd_impl(int op, const void* x, int64_t xs, const void* w, const void* b, vo
     pk = nullptr;
   if (pk != nullptr) {
     p.V = static_cast<int>(N * es / 16);
-    const size_t smem = static_cast<size_t>(pk->warps_m) * pk->stages * p.V * 16;  // the row slots
-    int occ;
-    if (int rc = occupancy(*dev, pk->fn, pk->threads(), smem, &occ)) return rc;
+    // the row slots (half a row each on a CTA pair)
+    const size_t smem = static_cast<size_t>(pk->warps_m) * pk->stages * (p.V / pk->cluster) * 16;
+    int occ;  // resident CTAs per SM, or resident clusters per device
+    if (int rc = occupancy(*dev, pk->fn, pk->threads(), smem, &occ, pk->cluster)) return rc;
+    const int64_t resident = (pk->cluster > 1) ? occ : (int64_t)dev->sm_count * occ;
     const int64_t want = (M + pk->warps_m - 1) / pk->warps_m;
-    const int grid = static_cast<int>(std::min<int64_t>(want, (int64_t)dev->sm_count * occ));
-    return launch(pk->fn, dim3(grid), dim3(pk->threads()), smem, &p, static_cast<cudaStream_t>(stream));
+    const int units = static_cast<int>(std::min<int64_t>(want, resident));
+    return launch(pk->fn, dim3(units * pk->cluster), dim3(pk->threads()), smem, &p, static_cast<cudaStream_t>(stream),
+                  true, pk->cluster);
   }
   int occ;
   if (int rc = occupancy(*dev, k->fwd_any[op], 256, 0, &occ)) return rc;

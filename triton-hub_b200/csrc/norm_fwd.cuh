@@ -45,9 +45,21 @@ struct FwdParams {
 // E[x^2]-E[x]^2.
 //
 // MINB is the number of CTAs per SM the register allocation must leave room for.
-template <typename T, int LDGS, int WARPS_M, int WARPS_N, bool PREG, int STAGES, int MINB, bool RMS>
+//
+// CL == 2: rows of 32 - 64 KB.  Launched in clusters of two CTAs; each CTA of a pair holds one
+// half of the columns of every row the pair owns (so weight and bias still fit in registers) and
+// the halves' statistics are swapped through distributed shared memory and merged in rank order.
+template <typename T, int LDGS, int WARPS_M, int WARPS_N, bool PREG, int STAGES, int MINB, int CL, bool RMS>
 __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(const FwdParams p) {
+  static_assert(CL == 1 || (CL == 2 && WARPS_M == 1), "cluster split: one row group per CTA");
   constexpr int VEC = Pack16<T>::kElems;
+  __shared__ float pair_box[2][2];  // CL == 2: the partner's statistics, double-buffered
+  const uint32_t cr = (CL > 1) ? cluster_cta_rank() : 0u;
+  const int unit = (CL > 1) ? static_cast<int>(blockIdx.x) / CL : static_cast<int>(blockIdx.x);
+  const int units = static_cast<int>(gridDim.x) / CL;
+  const int Vl = p.V / CL;                   // packets of each row this CTA handles ...
+  const int v0 = static_cast<int>(cr) * Vl;  // ... starting at this one
+  int pair_buf = 0;
   constexpr int TPR = WARPS_N * 32;  // threads per row
   constexpr int NBAR = STAGES > 0 ? WARPS_M * STAGES : 1;
   extern __shared__ __align__(128) unsigned char dyn_smem[];  // (WARPS_M, STAGES, row bytes)
@@ -62,9 +74,9 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
 
   const T* xb = static_cast<const T*>(p.x);
   T* yb = static_cast<T*>(p.y);
-  const int64_t first = (int64_t)blockIdx.x * WARPS_M + warp_m;
-  const int64_t step = (int64_t)gridDim.x * WARPS_M;
-  const uint32_t row_bytes = static_cast<uint32_t>(p.V) * 16u;
+  const int64_t first = (int64_t)unit * WARPS_M + warp_m;
+  const int64_t step = (int64_t)units * WARPS_M;
+  const uint32_t row_bytes = static_cast<uint32_t>(Vl) * 16u;
   unsigned char* slots = dyn_smem + (size_t)warp_m * STAGES * row_bytes;
   uint64_t* bars = full_bar + (STAGES > 0 ? warp_m * STAGES : 0);
 
@@ -78,6 +90,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
   }
   grid_dependency_sync();  // nothing above reads global memory
   trigger_dependents();
+  if (CL > 1) cluster_sync_all();  // the partner CTA is running: its shared memory may be written
   if (STAGES > 0) {
     if (t == 0) {
 #pragma unroll
@@ -85,7 +98,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
         const int64_t r = first + s * step;
         if (r < p.M) {
           mbar_expect_tx(&bars[s], row_bytes);
-          bulk_load(slots + (size_t)s * row_bytes, xb + r * p.x_stride, row_bytes, &bars[s]);
+          bulk_load(slots + (size_t)s * row_bytes, xb + r * p.x_stride + (size_t)v0 * VEC, row_bytes, &bars[s]);
         }
       }
     }
@@ -101,22 +114,22 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
       wr[j][e] = 1.f;
       br[j][e] = 0.f;
     }
-    if (PREG && v < p.V) {
+    if (PREG && v < Vl) {
       if (p.w != nullptr) {
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) wr[j][e] = load_param(p.w, p.w_dtype, (int64_t)v * VEC + e);
+        for (int e = 0; e < VEC; ++e) wr[j][e] = load_param(p.w, p.w_dtype, (int64_t)(v0 + v) * VEC + e);
       }
       if (!RMS && p.b != nullptr) {
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) br[j][e] = load_param(p.b, p.w_dtype, (int64_t)v * VEC + e);
+        for (int e = 0; e < VEC; ++e) br[j][e] = load_param(p.b, p.w_dtype, (int64_t)(v0 + v) * VEC + e);
       }
     }
   }
 
   const float inv_n = 1.f / static_cast<float>(p.N);
-  const bool uniform = (p.V % TPR) == 0 && p.V >= TPR;  // every thread of a row group holds the same element count
+  const bool uniform = (Vl % TPR) == 0 && Vl >= TPR;  // every thread of a row group holds the same element count
   // uniform rows: each thread holds V / TPR packets
-  const float thread_cnt = static_cast<float>((p.V / TPR) * VEC);
+  const float thread_cnt = static_cast<float>((Vl / TPR) * VEC);
   const float thread_inv_cnt = 1.f / (thread_cnt > 0.f ? thread_cnt : 1.f);
   int slot = 0;
   uint32_t parity = 0;
@@ -130,16 +143,16 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
       for (int j = 0; j < LDGS; ++j) {
         const int v = j * TPR + t;
         uint4 pk = make_uint4(0, 0, 0, 0);
-        if (v < p.V) pk = ld_shared16(srow + v);
+        if (v < Vl) pk = ld_shared16(srow + v);
         Pack16<T>::unpack(pk, xf[j]);
       }
     } else {
-      const uint4* xrow = reinterpret_cast<const uint4*>(xb + row * p.x_stride);
+      const uint4* xrow = reinterpret_cast<const uint4*>(xb + row * p.x_stride) + v0;
 #pragma unroll
       for (int j = 0; j < LDGS; ++j) {
         const int v = j * TPR + t;
         uint4 pk = make_uint4(0, 0, 0, 0);
-        if (v < p.V) pk = ld_stream(xrow + v);
+        if (v < Vl) pk = ld_stream(xrow + v);
         Pack16<T>::unpack(pk, xf[j]);
       }
     }
@@ -158,7 +171,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
         mean = s[0] * thread_inv_cnt;
 #pragma unroll
         for (int j = 0; j < LDGS; ++j) {
-          const bool live = (j * TPR + t) < p.V;
+          const bool live = (j * TPR + t) < Vl;
 #pragma unroll
           for (int e = 0; e < VEC; ++e) {
             const float d = live ? (xf[j][e] - mean) : 0.f;
@@ -166,10 +179,26 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
           }
         }
         group_moments<WARPS_N>(cnt, mean, q[0], red_smem[warp_m], phase, warp_m, warp_n, lane);
+        if (CL > 1) {  // merge the two halves (equal counts), rank 0's first
+          const float mine[2] = {mean, q[0]};
+          float theirs[2];
+          pair_swap<2>(mine, theirs, pair_box, pair_buf, cr);
+          const float m0 = cr == 0 ? mine[0] : theirs[0], m1 = cr == 0 ? theirs[0] : mine[0];
+          const float q0 = cr == 0 ? mine[1] : theirs[1], q1 = cr == 0 ? theirs[1] : mine[1];
+          const float d = m1 - m0;
+          mean = 0.5f * (m0 + m1);
+          q[0] = (q0 + q1) + d * d * (0.5f * cnt);
+        }
       } else {
         // Ragged rows (threads hold different element counts): the reference's two passes,
         // mean first, then the centred sum of squares (layernorm.py:32-35).
         group_sum<WARPS_N, 1>(s, red_smem[warp_m], phase, warp_m, warp_n, lane);
+        if (CL > 1) {
+          const float mine[2] = {s[0], 0.f};
+          float theirs[2];
+          pair_swap<2>(mine, theirs, pair_box, pair_buf, cr);
+          s[0] = cr == 0 ? mine[0] + theirs[0] : theirs[0] + mine[0];
+        }
         mean = s[0] * inv_n;
       }
     } else {
@@ -178,6 +207,12 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
 #pragma unroll
         for (int e = 0; e < VEC; ++e) q[0] += xf[j][e] * xf[j][e];
       group_sum<WARPS_N, 1>(q, red_smem[warp_m], phase, warp_m, warp_n, lane);
+      if (CL > 1) {
+        const float mine[2] = {q[0], 0.f};
+        float theirs[2];
+        pair_swap<2>(mine, theirs, pair_box, pair_buf, cr);
+        q[0] = cr == 0 ? mine[0] + theirs[0] : theirs[0] + mine[0];
+      }
     }
     if (STAGES > 0) {
       // Every thread of the group has its packets in registers: the slot can be refilled.
@@ -185,7 +220,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
         const int64_t r = row + STAGES * step;
         if (r < p.M) {
           mbar_expect_tx(&bars[slot], row_bytes);
-          bulk_load(slots + (size_t)slot * row_bytes, xb + r * p.x_stride, row_bytes, &bars[slot]);
+          bulk_load(slots + (size_t)slot * row_bytes, xb + r * p.x_stride + (size_t)v0 * VEC, row_bytes, &bars[slot]);
         }
       }
       if (++slot == STAGES) {
@@ -196,7 +231,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
     if (!RMS && !uniform) {
 #pragma unroll
       for (int j = 0; j < LDGS; ++j) {
-        const bool live = (j * TPR + t) < p.V;
+        const bool live = (j * TPR + t) < Vl;
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
           const float d = live ? (xf[j][e] - mean) : 0.f;
@@ -204,14 +239,20 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
         }
       }
       group_sum<WARPS_N, 1>(q, red_smem[warp_m], phase, warp_m, warp_n, lane);
+      if (CL > 1) {
+        const float mine[2] = {q[0], 0.f};
+        float theirs[2];
+        pair_swap<2>(mine, theirs, pair_box, pair_buf, cr);
+        q[0] = cr == 0 ? mine[0] + theirs[0] : theirs[0] + mine[0];
+      }
     }
     const float rstd = 1.f / sqrtf(q[0] * inv_n + p.eps);
-    if (t == 0) {
+    if (t == 0 && cr == 0) {
       if (!RMS) p.mean[row] = mean;
       p.rstd[row] = rstd;
     }
 
-    uint4* yrow = reinterpret_cast<uint4*>(yb + row * p.y_stride);
+    uint4* yrow = reinterpret_cast<uint4*>(yb + row * p.y_stride) + v0;
 #pragma unroll
     for (int j = 0; j < LDGS; ++j) {
       const int v = j * TPR + t;
@@ -219,13 +260,13 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
       if (PREG) {
 #pragma unroll
         for (int e = 0; e < VEC; ++e) yf[e] = (xf[j][e] - mean) * rstd * wr[j][e] + br[j][e];
-      } else if (v < p.V) {
-        if (p.w != nullptr) load_param_packet<T>(p.w, p.w_dtype, v, wr[0]);
-        if (!RMS && p.b != nullptr) load_param_packet<T>(p.b, p.w_dtype, v, br[0]);
+      } else if (v < Vl) {
+        if (p.w != nullptr) load_param_packet<T>(p.w, p.w_dtype, v0 + v, wr[0]);
+        if (!RMS && p.b != nullptr) load_param_packet<T>(p.b, p.w_dtype, v0 + v, br[0]);
 #pragma unroll
         for (int e = 0; e < VEC; ++e) yf[e] = (xf[j][e] - mean) * rstd * wr[0][e] + br[0][e];
       }
-      if (v < p.V) st_stream(yrow + v, Pack16<T>::pack(yf));
+      if (v < Vl) st_stream(yrow + v, Pack16<T>::pack(yf));
     }
   }
   if (STAGES > 0) {

@@ -112,6 +112,24 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// Swap NV floats with the partner CTA of a pair: `mine` goes into the partner's `box`, the
+// cluster barrier orders the two remote stores, and the partner's values are read from this
+// CTA's own `box`.  `box` is double-buffered by the caller (`buf` flips per call), so a CTA that
+// races ahead cannot overwrite values its partner has not read yet: a full cluster barrier lies
+// between two uses of the same buffer.
+template <int NV>
+__device__ __forceinline__ void pair_swap(const float (&mine)[NV], float (&theirs)[NV], float (*box)[NV], int& buf,
+                                          uint32_t cr) {
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) st_cluster_f32(cluster_map(smem_addr(&box[buf][i]), cr ^ 1u), mine[i]);
+  }
+  cluster_sync_all();
+#pragma unroll
+  for (int i = 0; i < NV; ++i) theirs[i] = box[buf][i];
+  buf ^= 1;
+}
+
 __device__ __forceinline__ uint4 ld_shared16(const void* p) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
