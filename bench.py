@@ -177,7 +177,8 @@ def run_gpu(args):
     wl_n = WORKLOADS[args.workload]["N"]
     if world > 1:
         from b200norm.parallel import GradExchange, PushExchange, sharded_layernorm_bwd, sharded_rmsnorm_bwd
-        exchange = (PushExchange(max_n=wl_n, slots=2, device=device, total_shards=8 if args.g_invariant else None)
+        exchange = (PushExchange(max_n=wl_n, slots=2, device=device, total_shards=8 if args.g_invariant else None,
+                                 device_numbering=args.graph)
                     if args.exchange == "push"
                     else GradExchange(mode=args.exchange))
 
@@ -234,16 +235,19 @@ def run_gpu(args):
 
     K = args.steps
     use_graph = args.graph and world == 1
+    # With several GPUs the step can still be graph-captured when the exchange is the library's own
+    # (no collective-library call inside): the kernels number the exchanges on the device.
+    use_graph_multi = args.graph and world > 1 and args.exchange == "push"
 
     # Eager pass: every step launched from Python, with an event pair around each kernel group.
     # It gives the per-kernel split for the roofline and, without --graph, the headline time.
-    KE = K if not use_graph else min(K, 50)
+    KE = K if not (use_graph or use_graph_multi) else min(K, 50)
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(KE)]
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    if not use_graph:
+    if not (use_graph or use_graph_multi):
         sampler.window[0] = time.perf_counter()
     start.record()
     prev = None
@@ -254,7 +258,7 @@ def run_gpu(args):
     finish(prev)
     stop.record()
     torch.cuda.synchronize()
-    if not use_graph:
+    if not (use_graph or use_graph_multi):
         sampler.window[1] = time.perf_counter()
     if world > 1:
         dist.barrier()
@@ -309,6 +313,30 @@ def run_gpu(args):
         torch.cuda.synchronize()
         fwd_ms = float(np.median([e[0].elapsed_time(e[1]) for e in sevs]))
         bwd_ms = float(np.median([e[1].elapsed_time(e[2]) for e in sevs]))
+    if use_graph_multi:
+        # One eager step opens the pipeline (push k); the captured step is
+        # [forward, backward + push k+1, finish k]; a last eager finish closes it.
+        _, pend = step()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            _, pend_next = step()
+            graph_out = finish(pend)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        sampler.window[0] = time.perf_counter()
+        start.record()
+        for _ in range(K):
+            graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        sampler.window[1] = time.perf_counter()
+        total_ms = start.elapsed_time(stop)
+        finish(pend_next)
+        torch.cuda.synchronize()
+        dist.barrier()
     if world > 1:
         t = torch.tensor([total_ms, fwd_ms, bwd_ms], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -357,7 +385,7 @@ def run_gpu(args):
             else "single GPU",
         },
         "launch_mode": ("cuda graph of one step (captured through the public wrappers), replayed per step"
-                        if use_graph else "eager: every kernel launched from Python"),
+                        if (use_graph or use_graph_multi) else "eager: every kernel launched from Python"),
         "eager_ms_per_step": round(eager_ms, 5),
         "rows_per_s": round(total_rows / (ms_per_step * 1e-3), 1),
         "frac_of_peak": round(value / world / peak, 4),

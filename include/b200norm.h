@@ -162,9 +162,11 @@ B200NORM_API int b200norm_finalize_dwdb(const float* group_sums, int groups, int
  *   w_dtype.  Same bits on every rank and as a single GPU summing the same shards.
  *
  * `seq` starts at 1 and grows by 1 per exchange on all ranks alike.  A rank must finish
- * exchange s before it starts exchange s + depth - 1 (depth >= 3), which keeps a slot from being
- * overwritten before a slower rank has read it.  inbox, flags and counter must be zero before
- * the first exchange.
+ * exchange s before it starts exchange s + depth - 1 (3 <= depth <= 8), which keeps a slot from
+ * being overwritten before a slower rank has read it.  Passing seq = 0 makes the kernels number
+ * the exchanges themselves from counters kept in `counter` (push and finish each count up from
+ * 1): nothing in the launch then changes from step to step, so a captured CUDA graph of the step
+ * can be replayed.  inbox, flags and counter (128 bytes) must be zero before the first exchange.
  */
 #define B200NORM_MAX_PEERS 8
 typedef struct b200norm_peers {
@@ -172,7 +174,7 @@ typedef struct b200norm_peers {
   size_t inbox_bytes;                   /* size of each rank's inbox */
   void* inbox[B200NORM_MAX_PEERS];      /* inbox[r]: rank r's inbox as mapped in THIS process */
   void* flags[B200NORM_MAX_PEERS];      /* flags[r]: rank r's (depth, world) u64 flags, likewise */
-  void* counter;                        /* this rank's own (depth,) u32 scratch */
+  void* counter;                        /* this rank's own 128 bytes of bookkeeping, zeroed once */
 } b200norm_peers;
 
 B200NORM_API int b200norm_ln_bwd_push(const void* x, int64_t x_row_stride, const void* dy, int64_t dy_row_stride,

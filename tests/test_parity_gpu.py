@@ -228,7 +228,7 @@ def test_fused_push_exchange_emulated_on_one_gpu(rms, world):
     lib = _lib.load()
     inbox_bytes = depth * S * slots * N * 4
     bufs = [torch.zeros(inbox_bytes + 256 * depth, dtype=torch.uint8, device=DEV) for _ in range(world)]
-    counters = [torch.zeros(depth, dtype=torch.int32, device=DEV) for _ in range(world)]
+    counters = [torch.zeros(32, dtype=torch.int32, device=DEV) for _ in range(world)]
     peers = []
     for r in range(world):
         pr = _lib.Peers()
@@ -280,7 +280,7 @@ def test_finish_kernel_gives_up_on_a_flag_nobody_sets():
     lib = _lib.load()
     inbox_bytes = depth * S * 1 * N * 4
     buf = torch.zeros(inbox_bytes + 256 * depth, dtype=torch.uint8, device=DEV)
-    counter = torch.zeros(depth, dtype=torch.int32, device=DEV)
+    counter = torch.zeros(32, dtype=torch.int32, device=DEV)
     pr = _lib.Peers()
     pr.world, pr.rank, pr.depth, pr.total_shards, pr.inbox_bytes = 1, 0, depth, S, inbox_bytes
     pr.inbox[0], pr.flags[0], pr.counter = buf.data_ptr(), buf.data_ptr() + inbox_bytes, counter.data_ptr()

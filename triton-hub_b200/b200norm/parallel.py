@@ -146,7 +146,8 @@ class PushExchange:
     """
 
     def __init__(self, max_n: int, slots: int = 2, group: Optional[dist.ProcessGroup] = None,
-                 total_shards: Optional[int] = None, depth: int = 4, device: Optional[torch.device] = None):
+                 total_shards: Optional[int] = None, depth: int = 4, device: Optional[torch.device] = None,
+                 device_numbering: bool = False):
         self.group = group if group is not None else (dist.group.WORLD if dist.is_initialized() else None)
         self.world = dist.get_world_size(self.group) if self.group is not None else 1
         self.rank = dist.get_rank(self.group) if self.group is not None else 0
@@ -162,9 +163,13 @@ class PushExchange:
         self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.inbox_bytes = depth * total_shards * slots * max_n * 4
         flag_bytes = (depth * max(self.world, 1) * 8 + 255) // 256 * 256
+        # device_numbering: the kernels count the exchanges themselves (seq = 0 in the ABI), so that a
+        # CUDA graph holding backward_* / finish calls can be replayed; the caller then keeps the
+        # "at most depth - 2 ahead" rule itself.
+        self.device_numbering = device_numbering
         self._seq = 0
         self._oldest_open = 1
-        self.counter = torch.zeros(depth, dtype=torch.int32, device=self.device)
+        self.counter = torch.zeros(32, dtype=torch.int32, device=self.device)  # 128 bytes of bookkeeping
         if self.world == 1:
             self._buf = torch.zeros(self.inbox_bytes + flag_bytes, dtype=torch.uint8, device=self.device)
             bases = [self._buf.data_ptr()]
@@ -188,6 +193,8 @@ class PushExchange:
     def _next(self, slots, N):
         if N > self.max_n or slots > self.slots:
             raise ValueError(f"exchange of {slots} x {N} exceeds this PushExchange ({self.slots} x {self.max_n})")
+        if self.device_numbering:
+            return 0
         if self._seq + 1 - self._oldest_open > self.depth - 2:
             raise RuntimeError("too many exchanges in flight: finish() an older one first")
         self._seq += 1

@@ -263,8 +263,8 @@ size_t partial_bytes(int64_t P, int64_t N) {
 int check_peers(const b200norm_peers* peers, uint64_t seq, int slots, int64_t N, int row_shards) {
   if (peers->world < 1 || peers->world > B200NORM_MAX_PEERS || peers->rank < 0 || peers->rank >= peers->world)
     return fail(B200NORM_ERR_ARG, "peers: bad world / rank (%d / %d)", peers->world, peers->rank);
-  if (peers->depth < 3) return fail(B200NORM_ERR_ARG, "peers: depth must be >= 3 (got %d)", peers->depth);
-  if (seq == 0) return fail(B200NORM_ERR_ARG, "peers: sequence numbers start at 1");
+  if (peers->depth < 3 || peers->depth > 8)
+    return fail(B200NORM_ERR_ARG, "peers: depth must be 3..8 (got %d)", peers->depth);
   if (row_shards >= 1 && peers->world * row_shards != peers->total_shards)
     return fail(B200NORM_ERR_ARG, "peers: world %d x row_shards %d != total_shards %d", peers->world, row_shards,
                 peers->total_shards);
@@ -285,7 +285,7 @@ PeerTargets peer_targets(const b200norm_peers* peers) {
     t.inbox[r] = (r < peers->world) ? static_cast<float*>(peers->inbox[r]) : nullptr;
     t.flags[r] = (r < peers->world) ? static_cast<unsigned long long*>(peers->flags[r]) : nullptr;
   }
-  t.counter = static_cast<unsigned int*>(peers->counter);
+  t.local = static_cast<LocalState*>(peers->counter);
   t.world = peers->world; t.rank = peers->rank; t.depth = peers->depth; t.total_shards = peers->total_shards;
   t.slot_floats = peers->inbox_bytes / sizeof(float) / peers->depth;
   return t;
@@ -597,6 +597,7 @@ int b200norm_finalize_pushed(const b200norm_peers* peers, uint64_t seq, int slot
   p.out[0] = dw;
   p.out[1] = (slots == 2) ? db : nullptr;
   p.status = dev->status_dev;
+  p.local = static_cast<LocalState*>(peers->counter);
   p.seq = seq;
   p.world = peers->world; p.depth = peers->depth; p.total_shards = peers->total_shards;
   p.slot_floats = peers->inbox_bytes / sizeof(float) / peers->depth;

@@ -24,10 +24,20 @@ namespace b200norm {
 
 constexpr int kMaxPeers = 8;
 
+// This rank's private bookkeeping (the `counter` buffer of b200norm_peers, 128 bytes, zeroed once).
+// Keeping the sequence numbers on the device lets a captured CUDA graph be replayed: with seq == 0
+// the kernels number the exchanges themselves instead of taking the number from the host.
+struct LocalState {
+  unsigned int push_ctas[8];      // CTAs of the current push kernel that are done, per inbox slot
+  unsigned long long push_seq;    // last exchange pushed
+  unsigned long long fin_seq;     // last exchange finished
+  unsigned int fin_ctas;          // CTAs of the current finish kernel that are done
+};
+
 struct PeerTargets {
   float* inbox[kMaxPeers];                // peer r's inbox, mapped here
   unsigned long long* flags[kMaxPeers];   // peer r's flags (depth, world)
-  unsigned int* counter;                  // this rank's CTA counters (depth,), zero between uses
+  LocalState* local;                      // this rank's bookkeeping
   int world, rank, depth, total_shards;
   size_t slot_floats;  // fp32 capacity of one of the `depth` inbox slots (the same for every exchange)
 };
@@ -62,7 +72,9 @@ __global__ void __launch_bounds__(512) colreduce_push_kernel(const ColReducePush
   trigger_dependents();
   const float* part = p.part[slot];
   const bool live = col < p.N && part != nullptr;
-  const int buf = static_cast<int>(p.seq % static_cast<unsigned long long>(p.peers.depth));
+  // seq == 0: number the exchange from the device-side counter (read before any CTA can advance it)
+  const unsigned long long seq = p.seq != 0 ? p.seq : p.peers.local->push_seq + 1;
+  const int buf = static_cast<int>(seq % static_cast<unsigned long long>(p.peers.depth));
   const size_t buf_off = (size_t)buf * p.peers.slot_floats;
   for (int g = 0; g < p.row_shards; ++g) {
     float s = 0.f;
@@ -87,12 +99,13 @@ __global__ void __launch_bounds__(512) colreduce_push_kernel(const ColReducePush
   __syncthreads();
   if (tx == 0 && ty == 0) {
     const unsigned int total = gridDim.x * gridDim.y;
-    const unsigned int prev = atomicAdd(&p.peers.counter[buf], 1u);
+    const unsigned int prev = atomicAdd(&p.peers.local->push_ctas[buf], 1u);
     if (prev == total - 1) {
-      p.peers.counter[buf] = 0;  // ready for this slot's next use
+      p.peers.local->push_ctas[buf] = 0;  // ready for this slot's next use
+      p.peers.local->push_seq = seq;      // every CTA of this launch has read the old value by now
       __threadfence_system();
       for (int r = 0; r < p.peers.world; ++r)
-        st_release_sys(&p.peers.flags[r][(size_t)buf * p.peers.world + p.peers.rank], p.seq);
+        st_release_sys(&p.peers.flags[r][(size_t)buf * p.peers.world + p.peers.rank], seq);
     }
   }
 }
@@ -102,6 +115,7 @@ struct FinalizePushedParams {
   const unsigned long long* flags;  // this rank's flags
   void* out[2];
   int* status;
+  LocalState* local;
   unsigned long long seq;
   size_t slot_floats;
   int world, depth, total_shards, slots, N, w_dtype;
@@ -111,17 +125,18 @@ struct FinalizePushedParams {
 // flag; the wait is bounded (2 s): on expiry the device status word is set and the kernel goes
 // on with whatever the inbox holds, so the stream never hangs.
 __global__ void __launch_bounds__(256) finalize_pushed_kernel(const FinalizePushedParams p) {
-  const int buf = static_cast<int>(p.seq % static_cast<unsigned long long>(p.depth));
   grid_dependency_sync();
   trigger_dependents();
+  const unsigned long long seq = p.seq != 0 ? p.seq : p.local->fin_seq + 1;  // 0: device-side numbering
+  const int buf = static_cast<int>(seq % static_cast<unsigned long long>(p.depth));
   if (threadIdx.x < p.world) {
     const unsigned long long* f = p.flags + (size_t)buf * p.world + threadIdx.x;
-    if (ld_acquire_sys(f) < p.seq) {
+    if (ld_acquire_sys(f) < seq) {
       const unsigned long long t0 = global_ns();
       bool ok = false;
       while (!ok) {
 #pragma unroll 1
-        for (int i = 0; i < 64 && !ok; ++i) ok = ld_acquire_sys(f) >= p.seq;
+        for (int i = 0; i < 64 && !ok; ++i) ok = ld_acquire_sys(f) >= seq;
         if (!ok && global_ns() - t0 > kWaitLimitNs) {
           if (p.status != nullptr) *reinterpret_cast<volatile int*>(p.status) = 4;  // B200NORM_ERR_TIMEOUT
           break;
@@ -132,11 +147,20 @@ __global__ void __launch_bounds__(256) finalize_pushed_kernel(const FinalizePush
   __syncthreads();
   const int col = blockIdx.x * 256 + threadIdx.x;
   const int slot = blockIdx.y;
-  if (col >= p.N || p.out[slot] == nullptr) return;
-  const float* base = p.inbox + (size_t)buf * p.slot_floats + (size_t)slot * p.N + col;
-  float total = 0.f;
-  for (int g = 0; g < p.total_shards; ++g) total += __ldcg(base + (size_t)g * p.slots * p.N);  // L2: peers wrote it
-  store_param(p.out[slot], p.w_dtype, col, total);
+  if (col < p.N && p.out[slot] != nullptr) {
+    const float* base = p.inbox + (size_t)buf * p.slot_floats + (size_t)slot * p.N + col;
+    float total = 0.f;
+    for (int g = 0; g < p.total_shards; ++g) total += __ldcg(base + (size_t)g * p.slots * p.N);  // L2: peers wrote it
+    store_param(p.out[slot], p.w_dtype, col, total);
+  }
+  // The last CTA to finish records the exchange as done (every CTA has read fin_seq by then).
+  if (threadIdx.x == 0) {
+    const unsigned int total_ctas = gridDim.x * gridDim.y;
+    if (atomicAdd(&p.local->fin_ctas, 1u) == total_ctas - 1) {
+      p.local->fin_ctas = 0;
+      p.local->fin_seq = seq;
+    }
+  }
 }
 
 }  // namespace b200norm
