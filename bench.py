@@ -30,7 +30,8 @@ for p in (ROOT, ROOT / "triton-hub_b200"):
 import numpy as np
 import torch
 
-# BASELINE.json configs.  c2 (configs[1]) is the default: the configuration the metric is quoted on.
+# The benchmark workloads (c1 = the reference README's Quick Start shape).  c2 is the default: the
+# configuration the headline metric is quoted on.
 WORKLOADS = {
     "c1": dict(op="ln", dtype="fp32", M=200, N=128, eps=1e-6, mu=0.0, sigma=1.0,
                desc="LayerNorm fp32 (2,100,128)"),

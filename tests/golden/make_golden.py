@@ -96,7 +96,9 @@ def run_case(L, R, name, op, dtype, batch, N, eps, mu, sigma, has_w, has_b):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/Triton-Hub")
+    ref = sys.argv[1]
     sys.path.insert(0, ref)
     from TritonHub.Normalization import layernorm as L
     from TritonHub.Normalization import rmsnorm as R

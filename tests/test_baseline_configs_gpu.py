@@ -1,4 +1,4 @@
-"""The BASELINE.json configurations at their full sizes, through the module API.
+"""The benchmark configurations (c1 ... c5) at their full sizes, through the module API.
 
 The CPU oracle cannot finish these in seconds, so each is checked three ways:
   1. every row, against a chunked torch reference on the GPU evaluated in fp32 from the same

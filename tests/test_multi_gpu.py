@@ -1,6 +1,6 @@
 """Row-sharded backward on 2 (or more) GPUs against a single-GPU run: with the all_gather
 exchange and the same total number of row shards, dweight and dbias must be BIT-identical to the
-single-GPU result (BASELINE config 5 asks for this determinism check); with all_reduce they must
+single-GPU result (the 1048576 x 4096 multi-GPU workload asks for this determinism check); with all_reduce they must
 agree to fp32 rounding.  Skipped where fewer than 2 GPUs are visible."""
 import os
 import socket
