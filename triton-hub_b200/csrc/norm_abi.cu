@@ -206,11 +206,11 @@ int fwd_impl(int op, const void* x, int64_t xs, const void* w, const void* b, vo
   if (pk != nullptr) {
     p.V = static_cast<int>(N * es / 16);
     // the row slots (half a row each on a CTA pair)
-    const size_t smem = static_cast<size_t>(pk->warps_m) * pk->stages * (p.V / pk->cluster) * 16;
+    const size_t smem = static_cast<size_t>(pk->warps_m) * pk->stages * (p.V / pk->cluster) * 16;  // 0 unstaged
     int occ;  // resident CTAs per SM, or resident clusters per device
     if (int rc = occupancy(*dev, pk->fn, pk->threads(), smem, &occ, pk->cluster)) return rc;
     const int64_t resident = (pk->cluster > 1) ? occ : (int64_t)dev->sm_count * occ;
-    const int64_t want = (M + pk->warps_m - 1) / pk->warps_m;
+    const int64_t want = (M + pk->rows_per_cta() - 1) / pk->rows_per_cta();
     const int units = static_cast<int>(std::min<int64_t>(want, resident));
     return launch(pk->fn, dim3(units * pk->cluster), dim3(pk->threads()), smem, &p, static_cast<cudaStream_t>(stream),
                   true, pk->cluster);
@@ -247,10 +247,11 @@ int plan_bwd(DeviceState& dev, const DTypeKernels* k, int op, int64_t rows_per_s
   const int64_t Nl = N / pk->cluster;
   plan->smem = ((static_cast<size_t>(pk->warps_m) * Nl * sizeof(float) + 127) & ~static_cast<size_t>(127)) +
                static_cast<size_t>(pk->warps_m) * pk->stages * 2 * (Nl * es);
+  if (pk->lanes < 32) plan->smem = 0;  // the short-row kernels keep their sums in static shared memory
   int occ;  // resident CTAs per SM, or resident clusters per device
   if (int rc = occupancy(dev, pk->fn, pk->threads(), plan->smem, &occ, pk->cluster)) return rc;
   const int64_t resident = (pk->cluster > 1) ? occ : (int64_t)dev.sm_count * occ;
-  const int64_t want = std::max<int64_t>(1, (rows_per_shard + pk->warps_m - 1) / pk->warps_m);
+  const int64_t want = std::max<int64_t>(1, (rows_per_shard + pk->rows_per_cta() - 1) / pk->rows_per_cta());
   plan->ctas_per_shard = static_cast<int>(std::min<int64_t>(want, resident));  // units: CTAs or CTA pairs
   return B200NORM_OK;
 }

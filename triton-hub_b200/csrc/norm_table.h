@@ -11,9 +11,11 @@ struct PacketKernel {
   int ldgs, warps_m, warps_n;
   int stages;          // shared-memory slots per row group filled by bulk copies (0: none)
   int cluster;         // CTAs that share one row (1, or 2: column halves on a CTA pair)
+  int lanes;           // lanes of a warp that share one row (32, or fewer: short rows, several per warp)
   bool packet_params;  // re-reads weight / bias per row as 16-byte packets: they must be aligned
   const void* fn;
-  int capacity() const { return ldgs * 32 * warps_n * cluster; }  // packets per row it can hold
+  int capacity() const { return ldgs * lanes * warps_n * cluster; }  // packets per row it can hold
+  int rows_per_cta() const { return warps_m * (32 / lanes); }       // rows a CTA works on at a time
   int threads() const { return 32 * warps_m * warps_n; }
 };
 
