@@ -183,11 +183,38 @@ def run_gpu(args):
                     if args.exchange == "push"
                     else GradExchange(mode=args.exchange))
 
+    from b200norm import activations as Act
+    approx = {"gelu": "none", "gelu_tanh": "tanh"}.get(args.act)
+    op = "ln" if ln else "rms"
+    if approx is not None and world > 1:
+        raise SystemExit("--act is a single-GPU measurement")
+
     def step(timing=None):
         """forward + backward; with world > 1 also starts the dweight/dbias all-reduce on the
         side stream and returns its handle so that it overlaps the next step's launches."""
         if timing is not None:
             timing[0].record()
+        if approx is not None:
+            # norm -> GeLU (the reference's Quick Start pair): fused kernels, or the two steps one after the other
+            if args.unfused:
+                if ln:
+                    yy, mean, rstd = Fn._layernorm_fwd(x, w, b, eps)
+                else:
+                    yy, rstd = Fn._rmsnorm_fwd(x, w, eps)
+                    mean = None
+                z = Act._gelu_fwd(yy, approx)
+                if timing is not None:
+                    timing[1].record()
+                dyy = Act._gelu_bwd(yy, dy, approx)
+                res = (Fn._layernorm_bwd(x, dyy, w, b, mean, rstd, eps) if ln else Fn._rmsnorm_bwd(x, dyy, w, rstd, eps))
+            else:
+                z, mean, rstd = Act._norm_gelu_fwd(op, x, w, b, eps, approx)
+                if timing is not None:
+                    timing[1].record()
+                res = Act._norm_gelu_bwd(op, x, dy, w, b, mean, rstd, eps, approx)
+            if timing is not None:
+                timing[2].record()
+            return (z,) + tuple(res), None
         if ln:
             y, mean, rstd = Fn._layernorm_fwd(x, w, b, eps)
         else:
@@ -290,12 +317,29 @@ def run_gpu(args):
         # (+ column reduce) captured separately, an event between the two replays of each step.
         g_fwd, g_bwd = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
         with torch.cuda.graph(g_fwd):
-            if ln:
+            if approx is not None:
+                if args.unfused:
+                    if ln:
+                        gyy, gmean, grstd = Fn._layernorm_fwd(x, w, b, eps)
+                    else:
+                        gyy, grstd = Fn._rmsnorm_fwd(x, w, eps)
+                        gmean = None
+                    gy = Act._gelu_fwd(gyy, approx)
+                else:
+                    gy, gmean, grstd = Act._norm_gelu_fwd(op, x, w, b, eps, approx)
+            elif ln:
                 gy, gmean, grstd = Fn._layernorm_fwd(x, w, b, eps)
             else:
                 gy, grstd = Fn._rmsnorm_fwd(x, w, eps)
         with torch.cuda.graph(g_bwd):
-            if ln:
+            if approx is not None:
+                if args.unfused:
+                    gdyy = Act._gelu_bwd(gyy, dy, approx)
+                    gb_out = (Fn._layernorm_bwd(x, gdyy, w, b, gmean, grstd, eps) if ln
+                              else Fn._rmsnorm_bwd(x, gdyy, w, grstd, eps))
+                else:
+                    gb_out = Act._norm_gelu_bwd(op, x, dy, w, b, gmean, grstd, eps, approx)
+            elif ln:
                 gb_out = Fn._layernorm_bwd(x, dy, w, b, gmean, grstd, eps)
             else:
                 gb_out = Fn._rmsnorm_bwd(x, dy, w, grstd, eps)
@@ -350,7 +394,7 @@ def run_gpu(args):
     # End to end through the public module-level API with HOST buffers: pinned x / dy in,
     # y / dx / dweight [/ dbias] out, copies inside the timed region.
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and approx is None:
         e2e = run_e2e(wl, x, dy, w, b, rows, world, device, args)
 
     peak, peak_src = measured_peak()
@@ -358,6 +402,8 @@ def run_gpu(args):
     bwd_gbs = bwd_bytes / (bwd_ms * 1e-3) / 1e9
     fwd_gbs = fwd_bytes / (fwd_ms * 1e-3) / 1e9
     launches_per_step = 3 + (1 if world > 1 else 0)  # fwd, bwd, column reduce [, finalize]
+    if approx is not None and args.unfused:
+        launches_per_step += 2  # the two stand-alone GeLU kernels
     line = {
         "metric": "LN/RMSNorm fwd+bwd achieved HBM GB/s",
         "value": round(value, 1),
@@ -372,7 +418,10 @@ def run_gpu(args):
         "dtype": wl["dtype"] + " storage, fp32 arithmetic",
         "data": "synthetic (seeded normal draws with the workload's mean/std; no dataset is involved)",
         "config": {
-            "workload": f"{args.workload}: {wl['desc']} fwd+bwd, eps={eps}",
+            "workload": f"{args.workload}: {wl['desc']} fwd+bwd, eps={eps}"
+                        + ("" if approx is None else f", followed by GeLU({approx}) "
+                           + ("as separate kernels" if args.unfused else "fused into the norm kernels")
+                           + "; bytes counted as for the fused pair (y never stored)"),
             "rows_per_gpu": rows,
             "rows_total": total_rows,
             "dim": N,
@@ -589,6 +638,9 @@ def main():
     ap.add_argument("--graph", dest="graph", action="store_true", default=True,
                     help="time a CUDA-graph replay of the step (single GPU; default)")
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="time eager launches instead")
+    ap.add_argument("--act", default="none", choices=["none", "gelu", "gelu_tanh"],
+                    help="time norm -> GeLU (the reference's Quick Start pair) instead of the norm alone")
+    ap.add_argument("--unfused", action="store_true", help="with --act: run norm and GeLU as separate kernels")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

@@ -146,6 +146,44 @@ B200NORM_API int b200norm_finalize_dwdb(const float* group_sums, int groups, int
                            int w_dtype, void* stream);
 
 /*
+ * The activation that follows the norm in the reference's Quick Start (README.md:44-48):
+ * GeLU, erf or tanh form (TritonHub/Activations/gelu.py).
+ *
+ * b200norm_gelu_fwd / _bwd replace _gelu_fwd (gelu.py:31-49, kernel :12-29) and _gelu_bwd
+ *   (gelu.py:83-105, kernel :56-81): y = gelu(x); dx = dout * gelu'(x).  approximate: 0 = 'none'
+ *   (erf), 1 = 'tanh'.  Any alignment is accepted.
+ * b200norm_*_act_fwd / _bwd fuse it into the norm (the reference runs two kernels and writes the
+ *   normalised tensor to memory in between; these do not): forward writes z = act(norm(x)) and
+ *   the same mean / rstd; backward takes dz, rebuilds y = xhat*w + b from the row (hence `b`),
+ *   forms dy = dz * act'(y) rounded to the storage type, and continues as b200norm_*_bwd.  Rows
+ *   must be 16-byte aligned in base, stride and length (B200NORM_ERR_UNSUPPORTED otherwise: run
+ *   the two steps separately).  act = B200NORM_ACT_NONE makes them identical to the plain entry
+ *   points.
+ */
+enum b200norm_act { B200NORM_ACT_NONE = 0, B200NORM_ACT_GELU_ERF = 1, B200NORM_ACT_GELU_TANH = 2 };
+
+B200NORM_API int b200norm_gelu_fwd(const void* x, int64_t x_row_stride, void* y, int64_t y_row_stride, int64_t M,
+                                   int64_t N, int approximate, int io_dtype, void* stream);
+B200NORM_API int b200norm_gelu_bwd(const void* x, int64_t x_row_stride, const void* dout, int64_t dout_row_stride,
+                                   void* dx, int64_t dx_row_stride, int64_t M, int64_t N, int approximate,
+                                   int io_dtype, void* stream);
+B200NORM_API int b200norm_ln_act_fwd(const void* x, int64_t x_row_stride, const void* w, const void* b, void* z,
+                                     int64_t z_row_stride, float* mean, float* rstd, int64_t M, int64_t N,
+                                     float eps, int act, int io_dtype, int w_dtype, void* stream);
+B200NORM_API int b200norm_rms_act_fwd(const void* x, int64_t x_row_stride, const void* w, void* z,
+                                      int64_t z_row_stride, float* rstd, int64_t M, int64_t N, float eps, int act,
+                                      int io_dtype, int w_dtype, void* stream);
+B200NORM_API int b200norm_ln_act_bwd(const void* x, int64_t x_row_stride, const void* dz, int64_t dz_row_stride,
+                                     const void* w, const void* b, const float* mean, const float* rstd, void* dx,
+                                     int64_t dx_row_stride, void* dw, void* db, float* group_sums, int row_shards,
+                                     void* workspace, size_t workspace_bytes, int64_t M, int64_t N, int act,
+                                     int io_dtype, int w_dtype, void* stream);
+B200NORM_API int b200norm_rms_act_bwd(const void* x, int64_t x_row_stride, const void* dz, int64_t dz_row_stride,
+                                      const void* w, const float* rstd, void* dx, int64_t dx_row_stride, void* dw,
+                                      float* group_sums, int row_shards, void* workspace, size_t workspace_bytes,
+                                      int64_t M, int64_t N, int act, int io_dtype, int w_dtype, void* stream);
+
+/*
  * Multi-GPU exchange fused into the backward's column reduce.  (No counterpart in the reference,
  * which is single-GPU.)  One process per GPU; every rank owns an inbox of `depth` equal slots of
  * inbox_bytes / depth each -- a slot holds one exchange's (total_shards, slots, N) fp32 at its

@@ -211,3 +211,41 @@ API int oracle_norm_bwd(const float* x, int64_t xs, const float* dy, int64_t dys
   free(db_part);
   return 0;
 }
+
+/* ---- GeLU: the activation that follows the norm in the reference's Quick Start ----------- */
+
+/* One element of _gelu_kernel_fwd (TritonHub/Activations/gelu.py:20-28).  approx != 0: tanh form. */
+#define GELU_FWD(ACC, X)                                                                  \
+  (approx ? ({ ACC x_ = (X);                                                              \
+               ACC inner_ = (ACC)sqrt(2.0 / M_PI) * (x_ + (ACC)0.044715 * x_ * x_ * x_);  /* gelu.py:22 */ \
+               ACC e_ = (ACC)exp((double)((ACC)2 * inner_));                              /* gelu.py:23 */ \
+               ACC t_ = (e_ - (ACC)1) / (e_ + (ACC)1);                                    /* gelu.py:24 */ \
+               (ACC)0.5 * x_ * ((ACC)1 + t_); })                                          /* gelu.py:25 */ \
+          : ({ ACC x_ = (X);                                                              \
+               (ACC)0.5 * x_ * ((ACC)1 + (ACC)erf((double)(x_ / (ACC)sqrt(2.0)))); }))   /* gelu.py:27 */
+
+/* One element of the derivative in _gelu_kernel_bwd (gelu.py:67-79). */
+#define GELU_GRAD(ACC, X)                                                                 \
+  (approx ? ({ ACC x_ = (X);                                                              \
+               ACC k_ = (ACC)sqrt(2.0 / M_PI);                                            \
+               ACC g_ = k_ * (x_ + (ACC)0.044715 * x_ * x_ * x_);                         /* gelu.py:69 */ \
+               ACC e_ = (ACC)exp((double)((ACC)2 * g_));                                  /* gelu.py:70 */ \
+               ACC t_ = (e_ - (ACC)1) / (e_ + (ACC)1);                                    /* gelu.py:71 */ \
+               ACC gp_ = k_ * ((ACC)1 + (ACC)3 * (ACC)0.044715 * x_ * x_);                /* gelu.py:72 */ \
+               (ACC)0.5 * ((ACC)1 + t_ + x_ * ((ACC)1 - t_ * t_) * gp_); })               /* gelu.py:73 */ \
+          : ({ ACC x_ = (X);                                                              \
+               ACC cdf_ = (ACC)0.5 * ((ACC)1 + (ACC)erf((double)(x_ / (ACC)sqrt(2.0))));  /* gelu.py:76 */ \
+               ACC pdf_ = (ACC)exp((double)((ACC)-0.5 * x_ * x_)) / (ACC)sqrt(2.0 * M_PI);/* gelu.py:77 */ \
+               cdf_ + x_ * pdf_; }))                                                      /* gelu.py:78 */
+
+/* y = gelu(x) over n elements (_gelu_kernel_fwd, gelu.py:12-29). */
+API void oracle_gelu_fwd(const float* x, float* y, int64_t n, int approx, int acc64) {
+  for (int64_t i = 0; i < n; ++i)
+    y[i] = acc64 ? (float)GELU_FWD(double, (double)x[i]) : (float)GELU_FWD(float, x[i]);
+}
+
+/* dx = dout * gelu'(x) over n elements (_gelu_kernel_bwd, gelu.py:56-81). */
+API void oracle_gelu_bwd(const float* x, const float* dout, float* dx, int64_t n, int approx, int acc64) {
+  for (int64_t i = 0; i < n; ++i)
+    dx[i] = acc64 ? (float)((double)dout[i] * GELU_GRAD(double, (double)x[i])) : dout[i] * (float)GELU_GRAD(float, x[i]);
+}

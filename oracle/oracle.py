@@ -40,6 +40,10 @@ def _load():
         lib.oracle_norm_fwd.argtypes = [vp, i64, vp, vp, vp, vp, vp, i64, i64, f32, i32, i32]
         lib.oracle_norm_bwd.restype = i32
         lib.oracle_norm_bwd.argtypes = [vp, i64, vp, i64, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32]
+        lib.oracle_gelu_fwd.restype = None
+        lib.oracle_gelu_fwd.argtypes = [vp, vp, i64, i32, i32]
+        lib.oracle_gelu_bwd.restype = None
+        lib.oracle_gelu_bwd.argtypes = [vp, vp, vp, i64, i32, i32]
         lib.oracle_set_threads.argtypes = [i32]
         lib.oracle_get_threads.restype = i32
         _lib = lib
@@ -110,6 +114,32 @@ def norm_bwd(x, dy, w, mean, rstd, *, rms=False, programs=148, acc64=False):
     if rc != 0:
         raise RuntimeError(f"oracle_norm_bwd failed ({rc})")
     return dx, dw, db
+
+
+def gelu_fwd(x, approximate="none", *, acc64=False):
+    """y = gelu(x) (TritonHub/Activations/gelu.py:12-29); fp32 result, not yet rounded to the storage type."""
+    x = _as_f32(x)
+    y = np.empty_like(x)
+    _load().oracle_gelu_fwd(_p(x), _p(y), x.size, int(approximate == "tanh"), int(acc64))
+    return y
+
+
+def gelu_bwd(x, dout, approximate="none", *, acc64=False):
+    """dx = dout * gelu'(x) (gelu.py:56-81)."""
+    x, dout = _as_f32(x), _as_f32(dout)
+    dx = np.empty_like(x)
+    _load().oracle_gelu_bwd(_p(x), _p(dout), _p(dx), x.size, int(approximate == "tanh"), int(acc64))
+    return dx
+
+
+def norm_gelu(x, dz, w, b, eps, approximate, *, rms=False, programs=8, acc64=True):
+    """The LayerNorm -> GeLU pair of the reference's Quick Start, forward and backward, with nothing
+    rounded in between: z = gelu(norm(x)); dy = dz * gelu'(y); (dx, dw, db) = norm_bwd(dy)."""
+    y, mean, rstd = norm_fwd(x, w, None if rms else b, eps, rms=rms, acc64=acc64)
+    z = gelu_fwd(y, approximate, acc64=acc64)
+    dy = gelu_bwd(y, dz, approximate, acc64=acc64)
+    dx, dw, db = norm_bwd(x, dy, w, mean, rstd, rms=rms, programs=programs, acc64=acc64)
+    return {"z": z, "mean": mean, "rstd": rstd, "dx": dx, "dw": dw, "db": db}
 
 
 def rel_err(a, ref) -> float:

@@ -95,6 +95,72 @@ def run_case(L, R, name, op, dtype, batch, N, eps, mu, sigma, has_w, has_b):
     print(name, "ok", sum(v.nbytes for v in out.values()) // 1024, "KiB raw")
 
 
+# GeLU (TritonHub/Activations/gelu.py): name, dtype, M, N, approximate
+GELU_CASES = [
+    ("gelu_fp32_50x128_none", torch.float32, 50, 128, "none"),
+    ("gelu_fp32_50x128_tanh", torch.float32, 50, 128, "tanh"),
+    ("gelu_fp16_7x1000_none", torch.float16, 7, 1000, "none"),
+    ("gelu_bf16_4x4096_tanh", torch.bfloat16, 4, 4096, "tanh"),
+]
+# LayerNorm -> GeLU as in the Quick Start (README.md:44-48), forward and backward through both of the
+# reference's kernel pairs: name, dtype, batch, N, eps, approximate
+CHAIN_CASES = [
+    ("quickstart_ln_gelu_fp32_2x100x128_none", torch.float32, (2, 100), 128, 1e-6, "none"),
+    ("ln_gelu_bf16_8x4096_tanh", torch.bfloat16, (8,), 4096, 1e-6, "tanh"),
+]
+
+
+def run_gelu(G, name, dtype, M, N, approximate):
+    g = torch.Generator().manual_seed(1)
+    x = (2 * torch.randn(M, N, generator=g)).to(dtype)
+    dout = torch.randn(M, N, generator=g).to(dtype)
+    y, dx = torch.empty_like(x), torch.empty_like(x)
+    BLOCK = min(65536 // x.element_size(), next_pow2(N))
+    approx = approximate == "tanh"
+    G._gelu_kernel_fwd.fn[(M, 1)](x, x.stride(0), y, y.stride(0), N, BLOCK_SIZE=BLOCK, approx=approx)
+    G._gelu_kernel_bwd.fn[(M, 1)](x, x.stride(0), dout, dout.stride(0), dx, dx.stride(0), N, BLOCK_SIZE=BLOCK,
+                                  approx=approx)
+    out = {}
+    for key, t in (("x", x), ("dout", dout), ("y", y), ("dx", dx)):
+        k, v = store(t)
+        out[key + k] = v
+    out["meta"] = np.array(["gelu", str(dtype).replace("torch.", ""), approximate])
+    np.savez_compressed(HERE / f"{name}.npz", **out)
+    print(name, "ok")
+
+
+def run_chain(L, G, name, dtype, batch, N, eps, approximate):
+    g = torch.Generator().manual_seed(2)
+    M = int(np.prod(batch))
+    x = torch.randn(M, N, generator=g).to(dtype)
+    dz = torch.randn(M, N, generator=g).to(dtype)
+    w = (1 + 0.1 * torch.randn(N, generator=g)).to(dtype)
+    b = (0.1 * torch.randn(N, generator=g)).to(dtype)
+    BLOCK = min(65536 // x.element_size(), next_pow2(N))
+    approx = approximate == "tanh"
+    y, z, dy, dx = (torch.empty_like(x) for _ in range(4))
+    mean = torch.empty(M, dtype=torch.float32)
+    rstd = torch.empty(M, dtype=torch.float32)
+    L._layernorm_kernel_fwd.fn[(M,)](x, x.stride(0), y, y.stride(0), w, b, mean, rstd, eps, N, BLOCK_SIZE=BLOCK,
+                                     HAS_WEIGHT=True, HAS_BIAS=True)
+    G._gelu_kernel_fwd.fn[(M, 1)](y, y.stride(0), z, z.stride(0), N, BLOCK_SIZE=BLOCK, approx=approx)
+    G._gelu_kernel_bwd.fn[(M, 1)](y, y.stride(0), dz, dz.stride(0), dy, dy.stride(0), N, BLOCK_SIZE=BLOCK, approx=approx)
+    rpp = math.ceil(M / PROGRAMS)
+    dwp = torch.empty(PROGRAMS, N, dtype=torch.float32)
+    dbp = torch.empty(PROGRAMS, N, dtype=torch.float32)
+    L._layernorm_kernel_bwd.fn[(PROGRAMS,)](x, x.stride(0), dy, dy.stride(0), dx, dx.stride(0), w, b, dwp, dbp, mean,
+                                            rstd, eps, M, N, rpp, BLOCK_SIZE=BLOCK, HAS_WEIGHT=True, HAS_BIAS=True)
+    out = {}
+    for key, t in (("x", x), ("dz", dz), ("w", w), ("b", b), ("z", z), ("dx", dx),
+                   ("dw", dwp.sum(0).to(dtype)), ("db", dbp.sum(0).to(dtype))):
+        k, v = store(t)
+        out[key + k] = v
+    out["meta"] = np.array(["ln_gelu", str(dtype).replace("torch.", ""), str(eps), approximate,
+                            "x".join(map(str, batch))])
+    np.savez_compressed(HERE / f"{name}.npz", **out)
+    print(name, "ok")
+
+
 def main():
     if len(sys.argv) < 2:
         raise SystemExit("usage: make_golden.py /path/to/Triton-Hub")
@@ -102,8 +168,13 @@ def main():
     sys.path.insert(0, ref)
     from TritonHub.Normalization import layernorm as L
     from TritonHub.Normalization import rmsnorm as R
+    from TritonHub.Activations import gelu as G
     for case in CASES:
         run_case(L, R, *case)
+    for case in GELU_CASES:
+        run_gelu(G, *case)
+    for case in CHAIN_CASES:
+        run_chain(L, G, *case)
 
 
 if __name__ == "__main__":

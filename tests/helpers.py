@@ -7,7 +7,10 @@ import torch
 from oracle import oracle as O
 
 GOLDEN_DIR = Path(__file__).resolve().parent / "golden"
-GOLDEN = sorted(p.stem for p in GOLDEN_DIR.glob("*.npz"))
+_ALL_GOLDEN = sorted(p.stem for p in GOLDEN_DIR.glob("*.npz"))
+GOLDEN = [n for n in _ALL_GOLDEN if "gelu" not in n]                      # the norm kernels alone
+GOLDEN_GELU = [n for n in _ALL_GOLDEN if n.startswith("gelu_")]          # the reference's GeLU kernels alone
+GOLDEN_CHAIN = [n for n in _ALL_GOLDEN if "_gelu_" in n and not n.startswith("gelu_")]   # LayerNorm -> GeLU
 
 TORCH_DTYPE = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16, "fp64": torch.float64}
 SHORT = {"float32": "fp32", "float16": "fp16", "bfloat16": "bf16", "float64": "fp64"}
@@ -32,6 +35,21 @@ def load_golden(name):
             out[key] = bits.view(np.float32)
         else:
             out[key] = None
+    return out
+
+
+def load_golden_arrays(name):
+    """Generic loader for the GeLU and LayerNorm->GeLU vectors: dict of float32/float64 arrays + 'meta' list."""
+    z = np.load(GOLDEN_DIR / f"{name}.npz")
+    out = {"meta": [str(v) for v in z["meta"]]}
+    for key in z.files:
+        if key == "meta":
+            continue
+        if key.endswith("__bf16bits"):
+            out[key[:-10]] = (z[key].astype(np.uint32) << 16).view(np.float32)
+        else:
+            out[key] = z[key].astype(np.float64 if z[key].dtype == np.float64 else np.float32)
+    out["dtype"] = SHORT[out["meta"][1]]
     return out
 
 

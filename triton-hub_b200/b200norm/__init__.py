@@ -2,8 +2,10 @@
 CUDA kernels behind TritonHub's module and autograd.Function interface."""
 from .functional import (_layernorm_bwd, _layernorm_fwd, _rmsnorm_bwd, _rmsnorm_fwd, finalize_dwdb, layernorm,
                          rmsnorm)
+from .activations import GeLU, LayerNormGeLU, RMSNormGeLU, gelu, layernorm_gelu, rmsnorm_gelu
 from .hostio import HostPipeline
 from .modules import LayerNorm, RMSNorm
 
-__all__ = ['LayerNorm', 'RMSNorm', 'layernorm', 'rmsnorm', 'finalize_dwdb', 'HostPipeline']
+__all__ = ['LayerNorm', 'RMSNorm', 'layernorm', 'rmsnorm', 'finalize_dwdb', 'HostPipeline', 'GeLU', 'gelu',
+           'LayerNormGeLU', 'RMSNormGeLU', 'layernorm_gelu', 'rmsnorm_gelu']
 __version__ = '0.1.0'

@@ -17,6 +17,9 @@ OK, ERR_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT = range(5)
 # Storage type codes of enum b200norm_dtype.
 F32, F16, BF16, F64 = range(4)
 
+# Fused activation codes of enum b200norm_act.
+ACT_NONE, ACT_GELU_ERF, ACT_GELU_TANH = range(3)
+
 _c = ctypes
 _vp, _i64, _int, _f32, _sz = _c.c_void_p, _c.c_int64, _c.c_int, _c.c_float, _c.c_size_t
 
@@ -46,6 +49,14 @@ SIGNATURES = {
     "b200norm_rms_bwd": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _int, _vp, _sz, _i64, _i64,
                                 _int, _int, _vp]),
     "b200norm_finalize_dwdb": (_int, [_vp, _int, _int, _vp, _vp, _i64, _int, _vp]),
+    "b200norm_gelu_fwd": (_int, [_vp, _i64, _vp, _i64, _i64, _i64, _int, _int, _vp]),
+    "b200norm_gelu_bwd": (_int, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _int, _int, _vp]),
+    "b200norm_ln_act_fwd": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _f32, _int, _int, _int, _vp]),
+    "b200norm_rms_act_fwd": (_int, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _i64, _f32, _int, _int, _int, _vp]),
+    "b200norm_ln_act_bwd": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _int, _vp, _sz,
+                                   _i64, _i64, _int, _int, _int, _vp]),
+    "b200norm_rms_act_bwd": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _int, _vp, _sz, _i64, _i64,
+                                    _int, _int, _int, _vp]),
     "b200norm_ln_bwd_push": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _int, _vp, _sz, _i64, _i64, _int,
                                     _int, _pp, _u64, _vp]),
     "b200norm_rms_bwd_push": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _int, _vp, _sz, _i64, _i64, _int, _int,

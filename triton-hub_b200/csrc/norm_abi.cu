@@ -108,15 +108,23 @@ int occupancy(DeviceState& s, const void* fn, int threads, size_t smem, int* out
   return B200NORM_OK;
 }
 
-const DTypeKernels* kernels_for(int dtype) {
+// The kernel table of a storage type and a fused activation (0 none, 1 GeLU erf, 2 GeLU tanh).
+const DTypeKernels* kernels_for(int dtype, int act = 0) {
+#define B200NORM_PICK(name) \
+  return act == 0 ? kernels_##name##_act0() : act == 1 ? kernels_##name##_act1() : kernels_##name##_act2();
   switch (dtype) {
-    case B200NORM_F32: return kernels_f32();
-    case B200NORM_F16: return kernels_f16();
-    case B200NORM_BF16: return kernels_bf16();
-    case B200NORM_F64: return kernels_f64();
+    case B200NORM_F32: B200NORM_PICK(f32)
+    case B200NORM_F16: B200NORM_PICK(f16)
+    case B200NORM_BF16: B200NORM_PICK(bf16)
+    case B200NORM_F64: B200NORM_PICK(f64)
     default: return nullptr;
   }
+#undef B200NORM_PICK
 }
+
+bool valid_act(int act) { return act >= B200NORM_ACT_NONE && act <= B200NORM_ACT_GELU_TANH; }
+
+constexpr size_t kMaxSmemPerCta = 227 * 1024;  // opt-in dynamic + static shared memory of one sm_100 CTA
 
 bool valid_dtype(int d) { return d >= B200NORM_F32 && d <= B200NORM_F64; }
 
@@ -125,9 +133,30 @@ bool aligned16(const void* p, int64_t stride_elems, int es) {
 }
 
 // First table entry whose capacity covers a row of V packets, or null.
-const PacketKernel* pick(const PacketKernel* tab, int n, int64_t V) {
-  for (int i = 0; i < n; ++i)
-    if (tab[i].capacity() >= V && V % tab[i].cluster == 0) return &tab[i];
+// Dynamic shared memory of a backward launch, per CTA: (warps_m [+1 with a fused activation: the
+// bias]) x columns fp32 for the weights and the row-group sums, padded to 128 bytes, then the
+// x + dy row slots.  A CTA of a pair holds half of the columns.
+size_t bwd_smem_bytes(const PacketKernel& pk, int64_t N, int es, int act) {
+  if (pk.lanes < 32) return 0;  // the short-row kernels keep their sums in static shared memory
+  const int64_t Nl = N / pk.cluster;
+  return ((static_cast<size_t>(pk.warps_m + (act != 0 ? 1 : 0)) * Nl * sizeof(float) + 127) & ~static_cast<size_t>(127)) +
+         static_cast<size_t>(pk.warps_m) * pk.stages * 2 * (Nl * es);
+}
+
+// First table entry whose capacity covers a row of V packets (and, for a backward table, whose
+// shared memory fits), or null.
+const PacketKernel* pick(const PacketKernel* tab, int n, int64_t V, bool bwd = false, int64_t N = 0, int es = 0,
+                         int act = 0) {
+  // Tuning aid: B200NORM_FORCE_FWD / B200NORM_FORCE_BWD = index of the table entry to use when it can hold the row.
+  static const int forced[2] = {std::getenv("B200NORM_FORCE_FWD") ? std::atoi(std::getenv("B200NORM_FORCE_FWD")) : -1,
+                                std::getenv("B200NORM_FORCE_BWD") ? std::atoi(std::getenv("B200NORM_FORCE_BWD")) : -1};
+  const int f = forced[bwd ? 1 : 0];
+  if (f >= 0 && f < n && tab[f].capacity() >= V && V % tab[f].cluster == 0) return &tab[f];
+  for (int i = 0; i < n; ++i) {
+    if (tab[i].capacity() < V || V % tab[i].cluster != 0) continue;
+    if (bwd && bwd_smem_bytes(tab[i], N, es, act) + 2048 > kMaxSmemPerCta) continue;
+    return &tab[i];
+  }
   return nullptr;
 }
 
@@ -181,14 +210,15 @@ int check_common(int64_t M, int64_t N, int io_dtype, int w_dtype) {
 }
 
 int fwd_impl(int op, const void* x, int64_t xs, const void* w, const void* b, void* y, int64_t ys, float* mean,
-             float* rstd, int64_t M, int64_t N, float eps, int io_dtype, int w_dtype, void* stream) {
+             float* rstd, int64_t M, int64_t N, float eps, int io_dtype, int w_dtype, void* stream, int act = 0) {
   if (int rc = check_common(M, N, io_dtype, w_dtype)) return rc;
+  if (!valid_act(act)) return fail(B200NORM_ERR_ARG, "unknown activation code %d", act);
   if (M == 0) return B200NORM_OK;
   if (!x || !y || !rstd || (op == kLN && !mean)) return fail(B200NORM_ERR_ARG, "null x / y / mean / rstd");
   if (xs < N || ys < N) return fail(B200NORM_ERR_ARG, "row stride smaller than N");
   DeviceState* dev;
   if (int rc = device_state(&dev)) return rc;
-  const DTypeKernels* k = kernels_for(io_dtype);
+  const DTypeKernels* k = kernels_for(io_dtype, act);
   const int es = k->elem_size;
 
   FwdParams p;
@@ -215,6 +245,10 @@ int fwd_impl(int op, const void* x, int64_t xs, const void* w, const void* b, vo
     return launch(pk->fn, dim3(units * pk->cluster), dim3(pk->threads()), smem, &p, static_cast<cudaStream_t>(stream),
                   true, pk->cluster);
   }
+  if (act != 0)
+    return fail(B200NORM_ERR_UNSUPPORTED,
+                "a fused activation needs rows whose base, stride and length are multiples of 16 bytes; run the norm "
+                "and b200norm_gelu_fwd separately");
   int occ;
   if (int rc = occupancy(*dev, k->fwd_any[op], 256, 0, &occ)) return rc;
   const int grid = static_cast<int>(std::min<int64_t>(M, (int64_t)dev->sm_count * occ));
@@ -233,21 +267,16 @@ int any_ctas_per_shard(int64_t rows_per_shard) {
 }
 
 int plan_bwd(DeviceState& dev, const DTypeKernels* k, int op, int64_t rows_per_shard, int64_t N, bool packets,
-             BwdPlan* plan) {
+             BwdPlan* plan, int act = 0) {
   const int es = k->elem_size;
-  plan->pk = packets ? pick(k->bwd[op], k->n_bwd[op], N * es / 16) : nullptr;
+  plan->pk = packets ? pick(k->bwd[op], k->n_bwd[op], N * es / 16, true, N, es, act) : nullptr;
   if (plan->pk == nullptr) {
     plan->ctas_per_shard = any_ctas_per_shard(rows_per_shard);
     plan->smem = 0;
     return B200NORM_OK;
   }
   const PacketKernel* pk = plan->pk;
-  // per CTA: fp32 weights / cross-group sums, padded to 128 bytes, then the x+dy row slots; a CTA
-  // of a pair holds half of each
-  const int64_t Nl = N / pk->cluster;
-  plan->smem = ((static_cast<size_t>(pk->warps_m) * Nl * sizeof(float) + 127) & ~static_cast<size_t>(127)) +
-               static_cast<size_t>(pk->warps_m) * pk->stages * 2 * (Nl * es);
-  if (pk->lanes < 32) plan->smem = 0;  // the short-row kernels keep their sums in static shared memory
+  plan->smem = bwd_smem_bytes(*pk, N, es, act);
   int occ;  // resident CTAs per SM, or resident clusters per device
   if (int rc = occupancy(dev, pk->fn, pk->threads(), plan->smem, &occ, pk->cluster)) return rc;
   const int64_t resident = (pk->cluster > 1) ? occ : (int64_t)dev.sm_count * occ;
@@ -295,8 +324,10 @@ PeerTargets peer_targets(const b200norm_peers* peers) {
 int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, const void* w, const float* mean,
              const float* rstd, void* dx, int64_t dxs, void* dw, void* db, float* group_sums, int row_shards,
              void* workspace, size_t workspace_bytes, int64_t M, int64_t N, int io_dtype, int w_dtype,
-             void* stream_v, const b200norm_peers* peers = nullptr, uint64_t seq = 0) {
+             void* stream_v, const b200norm_peers* peers = nullptr, uint64_t seq = 0, int act = 0,
+             const void* bias = nullptr) {
   if (int rc = check_common(M, N, io_dtype, w_dtype)) return rc;
+  if (!valid_act(act)) return fail(B200NORM_ERR_ARG, "unknown activation code %d", act);
   if (peers != nullptr) {
     if (int rc = check_peers(peers, seq, (op == kLN) ? 2 : 1, N, row_shards)) return rc;
   }
@@ -310,19 +341,23 @@ int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, con
   if (M == 0 && !want_params) return B200NORM_OK;
   DeviceState* dev;
   if (int rc = device_state(&dev)) return rc;
-  const DTypeKernels* k = kernels_for(io_dtype);
+  const DTypeKernels* k = kernels_for(io_dtype, act);
   const int es = k->elem_size;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
   const bool packets =
       (N * es) % 16 == 0 && aligned16(x, xs, es) && aligned16(dy, dys, es) && aligned16(dx, dxs, es);
   BwdPlan plan;
-  if (int rc = plan_bwd(*dev, k, op, M / row_shards, N, packets, &plan)) return rc;
+  if (int rc = plan_bwd(*dev, k, op, M / row_shards, N, packets, &plan, act)) return rc;
+  if (act != 0 && plan.pk == nullptr)
+    return fail(B200NORM_ERR_UNSUPPORTED,
+                "a fused activation needs rows whose base, stride and length are multiples of 16 bytes; run "
+                "b200norm_gelu_bwd and the norm's backward separately");
   const int64_t P = (int64_t)plan.ctas_per_shard * row_shards;
   const int slots = (op == kLN) ? 2 : 1;
 
   BwdParams p;
-  p.x = x; p.dy = dy; p.w = w; p.mean = mean; p.rstd = rstd; p.dx = dx;
+  p.x = x; p.dy = dy; p.w = w; p.b = bias; p.mean = mean; p.rstd = rstd; p.dx = dx;
   p.dw_part = nullptr; p.db_part = nullptr;
   p.x_stride = xs; p.dy_stride = dys; p.dx_stride = dxs;
   p.M = M; p.rows_per_shard = M / row_shards; p.ctas_per_shard = plan.ctas_per_shard;
@@ -375,6 +410,33 @@ int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, con
   c.N = static_cast<int>(N); c.w_dtype = w_dtype;
   return launch(reinterpret_cast<const void*>(&colreduce_kernel), dim3(static_cast<unsigned>((N + 31) / 32), slots),
                 dim3(32, 16), 0, &c, stream);
+}
+
+// Stand-alone GeLU (TritonHub/Activations/gelu.py:31-49, 83-105): approximate 0 = erf form, 1 = tanh form.
+int act_impl(bool bwd, const void* x, int64_t xs, const void* dout, int64_t ds, void* out, int64_t os, int64_t M,
+             int64_t N, int approximate, int io_dtype, void* stream) {
+  if (!valid_dtype(io_dtype)) return fail(B200NORM_ERR_ARG, "unknown dtype code %d", io_dtype);
+  if (approximate != 0 && approximate != 1) return fail(B200NORM_ERR_ARG, "approximate must be 0 (erf) or 1 (tanh)");
+  if (M < 0 || N < 1) return fail(B200NORM_ERR_ARG, "bad shape M=%lld N=%lld", (long long)M, (long long)N);
+  if (M == 0) return B200NORM_OK;
+  if (!x || !out || (bwd && !dout)) return fail(B200NORM_ERR_ARG, "null x / dout / output");
+  if (xs < N || os < N || (bwd && ds < N)) return fail(B200NORM_ERR_ARG, "row stride smaller than N");
+  DeviceState* dev;
+  if (int rc = device_state(&dev)) return rc;
+  const DTypeKernels* k = kernels_for(io_dtype, approximate == 0 ? B200NORM_ACT_GELU_ERF : B200NORM_ACT_GELU_TANH);
+  const int es = k->elem_size;
+  ActParams p;
+  p.x = x; p.dout = dout; p.out = out;
+  p.x_stride = xs; p.dout_stride = ds; p.out_stride = os;
+  p.M = M; p.N = static_cast<int>(N); p.V = static_cast<int>(N * es / 16);
+  const bool packets = (N * es) % 16 == 0 && aligned16(x, xs, es) && aligned16(out, os, es) &&
+                       (!bwd || aligned16(dout, ds, es));
+  const void* fn = packets ? k->act_packet[bwd ? 1 : 0] : k->act_any[bwd ? 1 : 0];
+  const int64_t work = packets ? M * p.V : M * N;  // threads' worth of items
+  int occ;
+  if (int rc = occupancy(*dev, fn, 256, 0, &occ)) return rc;
+  const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>((work + 255) / 256, (int64_t)dev->sm_count * occ)));
+  return launch(fn, dim3(grid), dim3(256), 0, &p, static_cast<cudaStream_t>(stream), packets);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -445,7 +507,7 @@ int rms_bwd_static_impl(const void* x, int64_t xs, const void* dy, int64_t dys, 
                 partial_bytes(P, N), (long long)P, (long long)N, kStaticScratchBytes);
 
   BwdParams p;
-  p.x = x; p.dy = dy; p.w = w; p.mean = nullptr; p.rstd = rstd; p.dx = dx;
+  p.x = x; p.dy = dy; p.w = w; p.b = nullptr; p.mean = nullptr; p.rstd = rstd; p.dx = dx;
   p.dw_part = (dw != nullptr) ? static_cast<float*>(st->scratch) : nullptr;
   p.db_part = nullptr;
   p.x_stride = xs; p.dy_stride = dys; p.dx_stride = dxs;
@@ -517,11 +579,13 @@ size_t b200norm_bwd_workspace_bytes(int64_t M, int64_t N, int io_dtype, int row_
   int64_t per_shard = any_ctas_per_shard(rps);
   if ((N * k->elem_size) % 16 == 0) {
     // LayerNorm and RMSNorm instantiations may differ in occupancy: take the larger.
-    for (int op = 0; op < 2; ++op) {
-      BwdPlan plan;
-      if (plan_bwd(*dev, k, op, rps, N, true, &plan)) return 0;
-      per_shard = std::max<int64_t>(per_shard, plan.ctas_per_shard);
-    }
+    // and with or without a fused activation
+    for (int act = 0; act < 3; ++act)
+      for (int op = 0; op < 2; ++op) {
+        BwdPlan plan;
+        if (plan_bwd(*dev, kernels_for(io_dtype, act), op, rps, N, true, &plan, act)) return 0;
+        if (plan.pk != nullptr) per_shard = std::max<int64_t>(per_shard, plan.ctas_per_shard);
+      }
   }
   return 2 * partial_bytes(per_shard * row_shards, N);
 }
@@ -606,6 +670,48 @@ int b200norm_finalize_pushed(const b200norm_peers* peers, uint64_t seq, int slot
   return launch(reinterpret_cast<const void*>(&finalize_pushed_kernel),
                 dim3(static_cast<unsigned>((N + 255) / 256), slots), dim3(256), 0, &p,
                 static_cast<cudaStream_t>(stream));
+}
+
+int b200norm_ln_act_fwd(const void* x, int64_t x_row_stride, const void* w, const void* b, void* z,
+                        int64_t z_row_stride, float* mean, float* rstd, int64_t M, int64_t N, float eps, int act,
+                        int io_dtype, int w_dtype, void* stream) {
+  return fwd_impl(kLN, x, x_row_stride, w, b, z, z_row_stride, mean, rstd, M, N, eps, io_dtype, w_dtype, stream, act);
+}
+
+int b200norm_rms_act_fwd(const void* x, int64_t x_row_stride, const void* w, void* z, int64_t z_row_stride,
+                         float* rstd, int64_t M, int64_t N, float eps, int act, int io_dtype, int w_dtype,
+                         void* stream) {
+  return fwd_impl(kRMS, x, x_row_stride, w, nullptr, z, z_row_stride, nullptr, rstd, M, N, eps, io_dtype, w_dtype,
+                  stream, act);
+}
+
+int b200norm_ln_act_bwd(const void* x, int64_t x_row_stride, const void* dz, int64_t dz_row_stride, const void* w,
+                        const void* b, const float* mean, const float* rstd, void* dx, int64_t dx_row_stride,
+                        void* dw, void* db, float* group_sums, int row_shards, void* workspace,
+                        size_t workspace_bytes, int64_t M, int64_t N, int act, int io_dtype, int w_dtype,
+                        void* stream) {
+  return bwd_impl(kLN, x, x_row_stride, dz, dz_row_stride, w, mean, rstd, dx, dx_row_stride, dw, db, group_sums,
+                  row_shards, workspace, workspace_bytes, M, N, io_dtype, w_dtype, stream, nullptr, 0, act, b);
+}
+
+int b200norm_rms_act_bwd(const void* x, int64_t x_row_stride, const void* dz, int64_t dz_row_stride, const void* w,
+                         const float* rstd, void* dx, int64_t dx_row_stride, void* dw, float* group_sums,
+                         int row_shards, void* workspace, size_t workspace_bytes, int64_t M, int64_t N, int act,
+                         int io_dtype, int w_dtype, void* stream) {
+  return bwd_impl(kRMS, x, x_row_stride, dz, dz_row_stride, w, nullptr, rstd, dx, dx_row_stride, dw, nullptr,
+                  group_sums, row_shards, workspace, workspace_bytes, M, N, io_dtype, w_dtype, stream, nullptr, 0, act,
+                  nullptr);
+}
+
+int b200norm_gelu_fwd(const void* x, int64_t x_row_stride, void* y, int64_t y_row_stride, int64_t M, int64_t N,
+                      int approximate, int io_dtype, void* stream) {
+  return act_impl(false, x, x_row_stride, nullptr, 0, y, y_row_stride, M, N, approximate, io_dtype, stream);
+}
+
+int b200norm_gelu_bwd(const void* x, int64_t x_row_stride, const void* dout, int64_t dout_row_stride, void* dx,
+                      int64_t dx_row_stride, int64_t M, int64_t N, int approximate, int io_dtype, void* stream) {
+  return act_impl(true, x, x_row_stride, dout, dout_row_stride, dx, dx_row_stride, M, N, approximate, io_dtype,
+                  stream);
 }
 
 int b200norm_rms_bwd_static(const void* x, int64_t x_row_stride, const void* dy, int64_t dy_row_stride,

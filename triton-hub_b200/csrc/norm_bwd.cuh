@@ -3,6 +3,7 @@
 // that the column reduce in norm_colreduce.cuh finishes.
 #pragma once
 
+#include "norm_act.cuh"
 #include "norm_common.cuh"
 #include "norm_stage.cuh"
 
@@ -12,6 +13,7 @@ struct BwdParams {
   const void* x;
   const void* dy;
   const void* w;      // may be null
+  const void* b;      // bias: only read when an activation is fused (to rebuild y); may be null
   const float* mean;  // LayerNorm only
   const float* rstd;
   void* dx;
@@ -58,8 +60,13 @@ struct BwdParams {
 // of every row the pair owns, and the two halves of the row sums are swapped through distributed
 // shared memory (one remote store + one cluster barrier per row).  Both CTAs add the halves in
 // rank order, so they hold identical sums.  A "unit" below is the CTA (CL == 1) or the pair.
+//
+// ACT != 0: the incoming gradient is that of act(y), not of y.  y = xhat*w + b is rebuilt from the
+// row (the forward did not store it), the gradient is multiplied by act'(y) and repacked in the
+// storage type -- the precision a separate activation-backward kernel would have written it with
+// -- and the rest of the kernel runs unchanged on it.
 template <typename T, int LDGS, int WARPS_M, int WARPS_N, bool PREFETCH, int STAGES, bool KEEP, int MINB, int CL,
-          bool RMS>
+          int ACT, bool RMS>
 __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(const BwdParams p) {
   static_assert(CL == 1 || (CL == 2 && WARPS_M == 1 && STAGES > 0), "cluster split: one row group, staged rows");
   constexpr int VEC = Pack16<T>::kElems;
@@ -98,7 +105,9 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
 
   float* w_s = reinterpret_cast<float*>(dyn_smem);
   const uint32_t row_bytes = static_cast<uint32_t>(Vl) * 16u;
-  const size_t param_bytes = ((size_t)WARPS_M * Nl * sizeof(float) + 127) & ~(size_t)127;
+  // (WARPS_M, Nl) floats for the weights / later the row-group sums, then Nl floats of bias if fused
+  const size_t param_bytes = ((size_t)(WARPS_M + (ACT != kActNone ? 1 : 0)) * Nl * sizeof(float) + 127) & ~(size_t)127;
+  float* b_s = w_s + (size_t)WARPS_M * Nl;
   unsigned char* slots = dyn_smem + param_bytes + (size_t)warp_m * STAGES * 2 * row_bytes;
   uint64_t* bars = full_bar + (STAGES > 0 ? warp_m * STAGES : 0);
 
@@ -116,8 +125,10 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
   }
   grid_dependency_sync();  // nothing above reads global memory
   trigger_dependents();
-  for (int c = threadIdx.x; c < Nl; c += WARPS_M * TPR)
+  for (int c = threadIdx.x; c < Nl; c += WARPS_M * TPR) {
     w_s[c] = (p.w != nullptr) ? load_param(p.w, p.w_dtype, (int64_t)v0 * VEC + c) : 1.f;
+    if (ACT != kActNone) b_s[c] = (!RMS && p.b != nullptr) ? load_param(p.b, p.w_dtype, (int64_t)v0 * VEC + c) : 0.f;
+  }
   __syncthreads();
   if (CL > 1) cluster_sync_all();  // the partner CTA is running: its shared memory may be written
   if (STAGES > 0 && t == 0) {
@@ -182,6 +193,25 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
         if (v < Vl) {
           xv[j] = ld_shared16(sx + v);
           gv[j] = ld_shared16(sg + v);
+        }
+      }
+    }
+
+    if (ACT != kActNone) {
+      // dy = dz * act'(y), y rebuilt from the row; repacked in place of dz.
+#pragma unroll
+      for (int j = 0; j < LDGS; ++j) {
+        const int v = j * TPR + t;
+        if (v < Vl) {
+          float xf[VEC], gf[VEC];
+          Pack16<T>::unpack(xv[j], xf);
+          Pack16<T>::unpack(gv[j], gf);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) {
+            const float y = (xf[e] - mu) * rs * w_s[v * VEC + e] + b_s[v * VEC + e];
+            gf[e] *= act_grad<ACT>(y);
+          }
+          gv[j] = Pack16<T>::pack(gf);
         }
       }
     }

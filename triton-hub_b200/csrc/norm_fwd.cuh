@@ -2,6 +2,7 @@
 // (TritonHub/Normalization/rmsnorm.py:14-38) with the whole row held in registers.
 #pragma once
 
+#include "norm_act.cuh"
 #include "norm_common.cuh"
 #include "norm_stage.cuh"
 
@@ -49,7 +50,10 @@ struct FwdParams {
 // CL == 2: rows of 32 - 64 KB.  Launched in clusters of two CTAs; each CTA of a pair holds one
 // half of the columns of every row the pair owns (so weight and bias still fit in registers) and
 // the halves' statistics are swapped through distributed shared memory and merged in rank order.
-template <typename T, int LDGS, int WARPS_M, int WARPS_N, bool PREG, int STAGES, int MINB, int CL, bool RMS>
+//
+// ACT != 0: the activation that follows the norm (GeLU) is applied to y before the store, so the
+// normalised tensor never goes to memory on its own.
+template <typename T, int LDGS, int WARPS_M, int WARPS_N, bool PREG, int STAGES, int MINB, int CL, int ACT, bool RMS>
 __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(const FwdParams p) {
   static_assert(CL == 1 || (CL == 2 && WARPS_M == 1), "cluster split: one row group per CTA");
   constexpr int VEC = Pack16<T>::kElems;
@@ -265,6 +269,10 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
         if (!RMS && p.b != nullptr) load_param_packet<T>(p.b, p.w_dtype, v0 + v, br[0]);
 #pragma unroll
         for (int e = 0; e < VEC; ++e) yf[e] = (xf[j][e] - mean) * rstd * wr[0][e] + br[0][e];
+      }
+      if (ACT != kActNone && v < Vl) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) yf[e] = act_fwd<ACT>(yf[e]);
       }
       if (v < Vl) st_stream(yrow + v, Pack16<T>::pack(yf));
     }

@@ -20,7 +20,7 @@ __device__ __forceinline__ float lanes_sum(float v) {
   return v;
 }
 
-template <typename T, int LANES, int LDGS, bool RMS>
+template <typename T, int LANES, int LDGS, int ACT, bool RMS>
 __global__ void __launch_bounds__(kSmallWarps * 32) norm_fwd_small_kernel(const FwdParams p) {
   constexpr int VEC = Pack16<T>::kElems;
   constexpr int RPW = 32 / LANES;  // rows per warp
@@ -96,13 +96,16 @@ __global__ void __launch_bounds__(kSmallWarps * 32) norm_fwd_small_kernel(const 
       const int v = j * LANES + t;
       float yf[VEC];
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) yf[e] = (xf[j][e] - mean) * rstd * wr[j][e] + br[j][e];
+      for (int e = 0; e < VEC; ++e) {
+        yf[e] = (xf[j][e] - mean) * rstd * wr[j][e] + br[j][e];
+        if (ACT != kActNone) yf[e] = act_fwd<ACT>(yf[e]);
+      }
       if (valid && v < p.V) st_stream(yrow + v, Pack16<T>::pack(yf));
     }
   }
 }
 
-template <typename T, int LANES, int LDGS, bool RMS>
+template <typename T, int LANES, int LDGS, int ACT, bool RMS>
 __global__ void __launch_bounds__(kSmallWarps * 32) norm_bwd_small_kernel(const BwdParams p) {
   constexpr int VEC = Pack16<T>::kElems;
   constexpr int RPW = 32 / LANES;
@@ -113,7 +116,8 @@ __global__ void __launch_bounds__(kSmallWarps * 32) norm_bwd_small_kernel(const 
   grid_dependency_sync();
   trigger_dependents();
 
-  float wr[LDGS][VEC], dw[LDGS][VEC], db[LDGS][VEC];
+  constexpr int BL = ACT != kActNone ? LDGS : 1;  // the bias is only needed to rebuild y for a fused activation
+  float wr[LDGS][VEC], br[BL][VEC], dw[LDGS][VEC], db[LDGS][VEC];
 #pragma unroll
   for (int j = 0; j < LDGS; ++j) {
     const int v = j * LANES + t;
@@ -122,6 +126,10 @@ __global__ void __launch_bounds__(kSmallWarps * 32) norm_bwd_small_kernel(const 
       wr[j][e] = 1.f;
       dw[j][e] = db[j][e] = 0.f;
       if (v < p.V && p.w != nullptr) wr[j][e] = load_param(p.w, p.w_dtype, (int64_t)v * VEC + e);
+      if (ACT != kActNone) {
+        br[j][e] = 0.f;
+        if (!RMS && v < p.V && p.b != nullptr) br[j][e] = load_param(p.b, p.w_dtype, (int64_t)v * VEC + e);
+      }
     }
   }
   const int shard = blockIdx.x / p.ctas_per_shard;
@@ -155,6 +163,11 @@ __global__ void __launch_bounds__(kSmallWarps * 32) norm_bwd_small_kernel(const 
       float xf[VEC], gf[VEC];
       Pack16<T>::unpack(px, xf);
       Pack16<T>::unpack(pg, gf);
+      if (ACT != kActNone) {  // dy = dz * act'(y), rounded to the storage type like a separate kernel would
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) gf[e] *= act_grad<ACT>((xf[e] - mu) * rs * wr[j][e] + br[j][e]);
+        Pack16<T>::unpack(Pack16<T>::pack(gf), gf);
+      }
 #pragma unroll
       for (int e = 0; e < VEC; ++e) {  // masked packets and rows carry dy = 0: they add nothing
         xh[j][e] = (xf[e] - mu) * rs;

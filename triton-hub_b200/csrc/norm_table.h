@@ -26,14 +26,21 @@ struct DTypeKernels {
   int n_fwd[2];
   const PacketKernel* bwd[2];
   int n_bwd[2];
-  const void* fwd_any[2];
+  const void* fwd_any[2];       // any-alignment norm kernels (tables without a fused activation only)
   const void* bwd_dx_any[2];
   const void* bwd_dwdb_any[2];
+  const void* act_packet[2];    // stand-alone activation, [0] forward [1] backward (tables of an activation only)
+  const void* act_any[2];
 };
 
-const DTypeKernels* kernels_f32();
-const DTypeKernels* kernels_f16();
-const DTypeKernels* kernels_bf16();
-const DTypeKernels* kernels_f64();
+// One table per (storage type, fused activation: 0 none, 1 GeLU erf, 2 GeLU tanh).
+#define B200NORM_DECLARE_TABLES(name)      \
+  const DTypeKernels* kernels_##name##_act0(); \
+  const DTypeKernels* kernels_##name##_act1(); \
+  const DTypeKernels* kernels_##name##_act2();
+B200NORM_DECLARE_TABLES(f32)
+B200NORM_DECLARE_TABLES(f16)
+B200NORM_DECLARE_TABLES(bf16)
+B200NORM_DECLARE_TABLES(f64)
 
 }  // namespace b200norm
