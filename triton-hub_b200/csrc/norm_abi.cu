@@ -398,6 +398,10 @@ int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, con
     c.peers = peer_targets(peers);
     c.seq = seq;
     c.per_shard = plan.ctas_per_shard; c.row_shards = row_shards; c.slots = slots; c.N = static_cast<int>(N);
+    // inbox slots start 16-byte aligned when slot_floats is a multiple of 4
+    if (N % 4 == 0 && c.peers.slot_floats % 4 == 0)
+      return launch(reinterpret_cast<const void*>(&colreduce4_push_kernel),
+                    dim3(static_cast<unsigned>((N + 127) / 128), slots), dim3(32, 16), 0, &c, stream);
     return launch(reinterpret_cast<const void*>(&colreduce_push_kernel),
                   dim3(static_cast<unsigned>((N + 31) / 32), slots), dim3(32, 16), 0, &c, stream);
   }
@@ -408,6 +412,9 @@ int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, con
   c.group_sums = group_sums;
   c.per_shard = plan.ctas_per_shard; c.row_shards = row_shards; c.slots = slots;
   c.N = static_cast<int>(N); c.w_dtype = w_dtype;
+  if (N % 4 == 0 && (group_sums == nullptr || (reinterpret_cast<uintptr_t>(group_sums) & 15u) == 0))
+    return launch(reinterpret_cast<const void*>(&colreduce4_kernel), dim3(static_cast<unsigned>((N + 127) / 128), slots),
+                  dim3(32, 16), 0, &c, stream);
   return launch(reinterpret_cast<const void*>(&colreduce_kernel), dim3(static_cast<unsigned>((N + 31) / 32), slots),
                 dim3(32, 16), 0, &c, stream);
 }

@@ -52,6 +52,51 @@ __global__ void __launch_bounds__(512) colreduce_kernel(const ColReduceParams p)
   if (ty == 0 && live && p.out[slot] != nullptr) store_param(p.out[slot], p.w_dtype, col, total);
 }
 
+// The same reduction four columns at a time (N a multiple of 4: every partial row is then 16-byte
+// aligned).  A CTA covers 128 columns with 128-bit loads; per column the additions happen in exactly
+// the order of colreduce_kernel, so both produce the same bits.
+__global__ void __launch_bounds__(512) colreduce4_kernel(const ColReduceParams p) {
+  __shared__ float4 tile[16][33];
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int col = (blockIdx.x * 32 + tx) * 4;
+  const int slot = blockIdx.y;
+  grid_dependency_sync();
+  trigger_dependents();
+  const float* part = p.part[slot];
+  const bool live = col < p.N && part != nullptr;
+  float4 total = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int g = 0; g < p.row_shards; ++g) {
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live) {
+      const float* base = part + (size_t)g * p.per_shard * p.N + col;
+      for (int r = ty; r < p.per_shard; r += 16) {
+        const float4 v = *reinterpret_cast<const float4*>(base + (size_t)r * p.N);
+        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+      }
+    }
+    tile[ty][tx] = s;
+    __syncthreads();
+    if (ty == 0) {
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        const float4 v = tile[k][tx];
+        a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+      }
+      if (live && p.group_sums != nullptr)
+        *reinterpret_cast<float4*>(p.group_sums + ((size_t)g * p.slots + slot) * p.N + col) = a;
+      total.x += a.x; total.y += a.y; total.z += a.z; total.w += a.w;
+    }
+    __syncthreads();
+  }
+  if (ty == 0 && live && p.out[slot] != nullptr) {
+    store_param(p.out[slot], p.w_dtype, col, total.x);
+    store_param(p.out[slot], p.w_dtype, col + 1, total.y);
+    store_param(p.out[slot], p.w_dtype, col + 2, total.z);
+    store_param(p.out[slot], p.w_dtype, col + 3, total.w);
+  }
+}
+
 // dweight / dbias from gathered shard sums (groups, slots, N): left-to-right add, then cast.
 struct FinalizeParams {
   const float* group_sums;

@@ -110,6 +110,58 @@ __global__ void __launch_bounds__(512) colreduce_push_kernel(const ColReducePush
   }
 }
 
+// Four columns at a time (N a multiple of 4): 128-bit loads of the partial rows and 128-bit remote
+// stores, a quarter of the CTAs (and of the fences and flag traffic).  Same per-column order.
+__global__ void __launch_bounds__(512) colreduce4_push_kernel(const ColReducePushParams p) {
+  __shared__ float4 tile[16][33];
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int col = (blockIdx.x * 32 + tx) * 4;
+  const int slot = blockIdx.y;
+  grid_dependency_sync();
+  trigger_dependents();
+  const float* part = p.part[slot];
+  const bool live = col < p.N && part != nullptr;
+  const unsigned long long seq = p.seq != 0 ? p.seq : p.peers.local->push_seq + 1;
+  const int buf = static_cast<int>(seq % static_cast<unsigned long long>(p.peers.depth));
+  const size_t buf_off = (size_t)buf * p.peers.slot_floats;
+  for (int g = 0; g < p.row_shards; ++g) {
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live) {
+      const float* base = part + (size_t)g * p.per_shard * p.N + col;
+      for (int r = ty; r < p.per_shard; r += 16) {
+        const float4 v = *reinterpret_cast<const float4*>(base + (size_t)r * p.N);
+        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+      }
+    }
+    tile[ty][tx] = s;
+    __syncthreads();
+    if (ty == 0 && live) {
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        const float4 v = tile[k][tx];
+        a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+      }
+      const size_t off = buf_off + ((size_t)(p.peers.rank * p.row_shards + g) * p.slots + slot) * p.N + col;
+      for (int r = 0; r < p.peers.world; ++r) *reinterpret_cast<float4*>(p.peers.inbox[r] + off) = a;
+    }
+    __syncthreads();
+  }
+  if (ty == 0) __threadfence_system();
+  __syncthreads();
+  if (tx == 0 && ty == 0) {
+    const unsigned int total = gridDim.x * gridDim.y;
+    const unsigned int prev = atomicAdd(&p.peers.local->push_ctas[buf], 1u);
+    if (prev == total - 1) {
+      p.peers.local->push_ctas[buf] = 0;
+      p.peers.local->push_seq = seq;
+      __threadfence_system();
+      for (int r = 0; r < p.peers.world; ++r)
+        st_release_sys(&p.peers.flags[r][(size_t)buf * p.peers.world + p.peers.rank], seq);
+    }
+  }
+}
+
 struct FinalizePushedParams {
   const float* inbox;               // this rank's inbox
   const unsigned long long* flags;  // this rank's flags
