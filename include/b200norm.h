@@ -184,6 +184,22 @@ B200NORM_API int b200norm_rms_act_bwd(const void* x, int64_t x_row_stride, const
                                       int64_t M, int64_t N, int act, int io_dtype, int w_dtype, void* stream);
 
 /*
+ * Row-wise Softmax / LogSoftmax over the last dimension, the reference's other "row in registers
+ * + row reduction" kernels (TritonHub/Activations/softmax.py, logsoftmax.py; Softmin is Softmax of
+ * -x, softmin.py:103).  b200norm_softmax_fwd replaces _softmax_fwd / _logsoftmax_fwd
+ * (softmax.py:24-41, logsoftmax.py:26-48): y = exp(x - max) / sum exp(x - max), or its logarithm
+ * when log_softmax != 0.  b200norm_softmax_bwd replaces _softmax_bwd / _logsoftmax_bwd
+ * (softmax.py:64-84, logsoftmax.py:69-91); like them it takes the saved OUTPUT y, not x:
+ *   Softmax dx = y * (dout - sum(dout * y));  LogSoftmax dx = dout - exp(y) * sum(dout).
+ * fp32 arithmetic, any alignment, rows up to 64 KB.
+ */
+B200NORM_API int b200norm_softmax_fwd(const void* x, int64_t x_row_stride, void* y, int64_t y_row_stride, int64_t M,
+                                      int64_t N, int log_softmax, int io_dtype, void* stream);
+B200NORM_API int b200norm_softmax_bwd(const void* y, int64_t y_row_stride, const void* dout, int64_t dout_row_stride,
+                                      void* dx, int64_t dx_row_stride, int64_t M, int64_t N, int log_softmax,
+                                      int io_dtype, void* stream);
+
+/*
  * Multi-GPU exchange fused into the backward's column reduce.  (No counterpart in the reference,
  * which is single-GPU.)  One process per GPU; every rank owns an inbox of `depth` equal slots of
  * inbox_bytes / depth each -- a slot holds one exchange's (total_shards, slots, N) fp32 at its

@@ -249,3 +249,52 @@ API void oracle_gelu_bwd(const float* x, const float* dout, float* dx, int64_t n
   for (int64_t i = 0; i < n; ++i)
     dx[i] = acc64 ? (float)((double)dout[i] * GELU_GRAD(double, (double)x[i])) : dout[i] * (float)GELU_GRAD(float, x[i]);
 }
+
+/* ---- Softmax / LogSoftmax over rows -------------------------------------------------------- */
+
+/* _softmax_kernel_fwd (TritonHub/Activations/softmax.py:11-22) and _logsoftmax_kernel_fwd
+ * (logsoftmax.py:11-24), one program per row. */
+API void oracle_softmax_fwd(const float* x, float* y, int64_t M, int64_t N, int log_softmax, int acc64) {
+  for (int64_t r = 0; r < M; ++r) {
+    const float* xr = x + r * N;
+    float* yr = y + r * N;
+    float mx = -INFINITY;
+    for (int64_t c = 0; c < N; ++c) mx = xr[c] > mx ? xr[c] : mx;          /* softmax.py:19 */
+    if (acc64) {
+      double den = 0;
+      for (int64_t c = 0; c < N; ++c) den += exp((double)xr[c] - (double)mx); /* softmax.py:20-21 */
+      for (int64_t c = 0; c < N; ++c) {
+        const double z = (double)xr[c] - (double)mx;
+        yr[c] = (float)(log_softmax ? z - log(den) : exp(z) / den);        /* softmax.py:22, logsoftmax.py:21-22 */
+      }
+    } else {
+      float den = 0;
+      for (int64_t c = 0; c < N; ++c) den += expf(xr[c] - mx);
+      for (int64_t c = 0; c < N; ++c) {
+        const float z = xr[c] - mx;
+        yr[c] = log_softmax ? z - logf(den) : expf(z) / den;
+      }
+    }
+  }
+}
+
+/* _softmax_kernel_bwd (softmax.py:48-62) and _logsoftmax_kernel_bwd (logsoftmax.py:51-68); `y` is
+ * the forward's output (softmax.py:93-96). */
+API void oracle_softmax_bwd(const float* y, const float* dout, float* dx, int64_t M, int64_t N, int log_softmax,
+                            int acc64) {
+  for (int64_t r = 0; r < M; ++r) {
+    const float *yr = y + r * N, *gr = dout + r * N;
+    float* dr = dx + r * N;
+    if (acc64) {
+      double s = 0;
+      for (int64_t c = 0; c < N; ++c) s += log_softmax ? (double)gr[c] : (double)gr[c] * yr[c];
+      for (int64_t c = 0; c < N; ++c)
+        dr[c] = (float)(log_softmax ? (double)gr[c] - exp((double)yr[c]) * s      /* logsoftmax.py:63-65 */
+                                    : -(double)yr[c] * s + (double)gr[c] * yr[c]); /* softmax.py:59 */
+    } else {
+      float s = 0;
+      for (int64_t c = 0; c < N; ++c) s += log_softmax ? gr[c] : gr[c] * yr[c];
+      for (int64_t c = 0; c < N; ++c) dr[c] = log_softmax ? gr[c] - expf(yr[c]) * s : -yr[c] * s + gr[c] * yr[c];
+    }
+  }
+}

@@ -44,6 +44,10 @@ def _load():
         lib.oracle_gelu_fwd.argtypes = [vp, vp, i64, i32, i32]
         lib.oracle_gelu_bwd.restype = None
         lib.oracle_gelu_bwd.argtypes = [vp, vp, vp, i64, i32, i32]
+        lib.oracle_softmax_fwd.restype = None
+        lib.oracle_softmax_fwd.argtypes = [vp, vp, i64, i64, i32, i32]
+        lib.oracle_softmax_bwd.restype = None
+        lib.oracle_softmax_bwd.argtypes = [vp, vp, vp, i64, i64, i32, i32]
         lib.oracle_set_threads.argtypes = [i32]
         lib.oracle_get_threads.restype = i32
         _lib = lib
@@ -140,6 +144,24 @@ def norm_gelu(x, dz, w, b, eps, approximate, *, rms=False, programs=8, acc64=Tru
     dy = gelu_bwd(y, dz, approximate, acc64=acc64)
     dx, dw, db = norm_bwd(x, dy, w, mean, rstd, rms=rms, programs=programs, acc64=acc64)
     return {"z": z, "mean": mean, "rstd": rstd, "dx": dx, "dw": dw, "db": db}
+
+
+def softmax_fwd(x, *, log=False, acc64=False):
+    """Row-wise softmax / log-softmax of an (M, N) array (softmax.py:11-22, logsoftmax.py:11-24)."""
+    x = _as_f32(x)
+    M, N = x.shape
+    y = np.empty_like(x)
+    _load().oracle_softmax_fwd(_p(x), _p(y), M, N, int(log), int(acc64))
+    return y
+
+
+def softmax_bwd(y, dout, *, log=False, acc64=False):
+    """dx from the forward's OUTPUT y and dout (softmax.py:48-62, logsoftmax.py:51-68)."""
+    y, dout = _as_f32(y), _as_f32(dout)
+    M, N = y.shape
+    dx = np.empty_like(y)
+    _load().oracle_softmax_bwd(_p(y), _p(dout), _p(dx), M, N, int(log), int(acc64))
+    return dx
 
 
 def rel_err(a, ref) -> float:

@@ -110,6 +110,39 @@ CHAIN_CASES = [
 ]
 
 
+# Softmax family (TritonHub/Activations/softmax.py, logsoftmax.py): name, kind, dtype, M, N
+SOFTMAX_CASES = [
+    ("softmax_fp32_20x128", "softmax", torch.float32, 20, 128),
+    ("softmax_fp16_6x1000", "softmax", torch.float16, 6, 1000),
+    ("logsoftmax_fp32_9x333", "logsoftmax", torch.float32, 9, 333),
+    ("logsoftmax_bf16_4x4096", "logsoftmax", torch.bfloat16, 4, 4096),
+]
+
+
+def run_softmax(S, LS, name, kind, dtype, M, N):
+    g = torch.Generator().manual_seed(3)
+    x = (2 * torch.randn(M, N, generator=g)).to(dtype)
+    dout = torch.randn(M, N, generator=g).to(dtype)
+    y, dx = torch.empty_like(x), torch.empty_like(x)
+    BLOCK = min(65536 // x.element_size(), next_pow2(N))
+    if kind == "softmax":
+        S._softmax_kernel_fwd.fn[(M, 1)](x, x.stride(0), y, y.stride(0), N, BLOCK_SIZE=BLOCK)
+        S._softmax_kernel_bwd.fn[(M, 1)](y, y.stride(0), dout, dout.stride(0), dx, dx.stride(0), N, BLOCK_SIZE=BLOCK)
+    else:
+        import triton.language as tl
+        tdt = {torch.float32: tl.float32, torch.float16: tl.float16, torch.bfloat16: tl.bfloat16}[dtype]
+        LS._logsoftmax_kernel_fwd.fn[(M, 1)](x, x.stride(0), y, y.stride(0), N, BLOCK_SIZE=BLOCK, dtype=tdt)
+        LS._logsoftmax_kernel_bwd.fn[(M, 1)](y, y.stride(0), dout, dout.stride(0), dx, dx.stride(0), N,
+                                             BLOCK_SIZE=BLOCK, dtype=tdt)
+    out = {}
+    for key, t in (("x", x), ("dout", dout), ("y", y), ("dx", dx)):
+        k, v = store(t)
+        out[key + k] = v
+    out["meta"] = np.array([kind, str(dtype).replace("torch.", "")])
+    np.savez_compressed(HERE / f"{name}.npz", **out)
+    print(name, "ok")
+
+
 def run_gelu(G, name, dtype, M, N, approximate):
     g = torch.Generator().manual_seed(1)
     x = (2 * torch.randn(M, N, generator=g)).to(dtype)
@@ -175,6 +208,10 @@ def main():
         run_gelu(G, *case)
     for case in CHAIN_CASES:
         run_chain(L, G, *case)
+    from TritonHub.Activations import logsoftmax as LS
+    from TritonHub.Activations import softmax as S
+    for case in SOFTMAX_CASES:
+        run_softmax(S, LS, *case)
 
 
 if __name__ == "__main__":

@@ -5,7 +5,8 @@ from .functional import (_layernorm_bwd, _layernorm_fwd, _rmsnorm_bwd, _rmsnorm_
 from .activations import GeLU, LayerNormGeLU, RMSNormGeLU, gelu, layernorm_gelu, rmsnorm_gelu
 from .hostio import HostPipeline
 from .modules import LayerNorm, RMSNorm
+from .softmax import LogSoftmax, Softmax, Softmin
 
 __all__ = ['LayerNorm', 'RMSNorm', 'layernorm', 'rmsnorm', 'finalize_dwdb', 'HostPipeline', 'GeLU', 'gelu',
-           'LayerNormGeLU', 'RMSNormGeLU', 'layernorm_gelu', 'rmsnorm_gelu']
+           'LayerNormGeLU', 'RMSNormGeLU', 'layernorm_gelu', 'rmsnorm_gelu', 'Softmax', 'LogSoftmax', 'Softmin']
 __version__ = '0.1.0'

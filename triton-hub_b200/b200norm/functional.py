@@ -69,11 +69,12 @@ def _require_cuda(x: torch.Tensor) -> None:
 def _rows(x: torch.Tensor) -> torch.Tensor:
     """Flatten to (M, N) with unit column stride and a row stride the kernels accept."""
     if x.stride(-1) != 1:
-        x = x.contiguous()
+        x = x.contiguous()          # as the reference does (layernorm.py:49-50)
     x = x.reshape(-1, x.shape[-1])
-    assert x.stride(-1) == 1 or x.shape[-1] == 1 or x.shape[0] == 0, 'expect input to be row-major'
-    if x.shape[0] > 1 and x.stride(0) < x.shape[1] or x.shape[-1] == 1 and x.stride(-1) != 1:
-        x = x.contiguous()  # expanded / overlapping rows
+    M, N = x.shape
+    overlapping_rows = M > 1 and x.stride(0) < N      # e.g. an expanded tensor (row stride 0)
+    if overlapping_rows or (N > 1 and x.stride(-1) != 1):
+        x = x.contiguous()
     return x
 
 

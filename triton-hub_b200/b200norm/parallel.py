@@ -25,6 +25,7 @@ Three exchange paths:
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Callable, Optional, Sequence, Tuple
 
 import torch
@@ -224,5 +225,5 @@ class PushExchange:
 
 
 def ctypes_ref(struct):
-    import ctypes
+    """Pointer argument for a ctypes Structure (the b200norm_peers* of the C ABI)."""
     return ctypes.byref(struct)

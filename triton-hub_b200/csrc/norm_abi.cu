@@ -17,6 +17,7 @@
 #include "norm_fwd.cuh"
 #include "norm_push.cuh"
 #include "norm_table.h"
+#include "softmax.cuh"
 
 namespace b200norm {
 namespace {
@@ -446,6 +447,53 @@ int act_impl(bool bwd, const void* x, int64_t xs, const void* dout, int64_t ds, 
   return launch(fn, dim3(grid), dim3(256), 0, &p, static_cast<cudaStream_t>(stream), packets);
 }
 
+// Row-wise Softmax / LogSoftmax (TritonHub/Activations/softmax.py:24-41, 64-84; logsoftmax.py:26-48, 69-91).
+// Forward: x -> y.  Backward: the saved output y and dout -> dx.
+int softmax_impl(bool bwd, const void* x, int64_t xs, const void* dout, int64_t ds, void* out, int64_t os, int64_t M,
+                 int64_t N, int log_softmax, int io_dtype, void* stream) {
+  if (!valid_dtype(io_dtype)) return fail(B200NORM_ERR_ARG, "unknown dtype code %d", io_dtype);
+  if (log_softmax != 0 && log_softmax != 1) return fail(B200NORM_ERR_ARG, "log_softmax must be 0 or 1");
+  if (M < 0 || N < 1) return fail(B200NORM_ERR_ARG, "bad shape M=%lld N=%lld", (long long)M, (long long)N);
+  const SoftmaxTable* k = io_dtype == B200NORM_F32   ? softmax_kernels_f32()
+                          : io_dtype == B200NORM_F16 ? softmax_kernels_f16()
+                          : io_dtype == B200NORM_BF16 ? softmax_kernels_bf16()
+                                                      : softmax_kernels_f64();
+  const int es = k->elem_size;
+  if (N * es > kMaxRowBytes)
+    return fail(B200NORM_ERR_UNSUPPORTED, "softmax rows wider than 64KB are not supported (N=%lld)", (long long)N);
+  if (M == 0) return B200NORM_OK;
+  if (!x || !out || (bwd && !dout)) return fail(B200NORM_ERR_ARG, "null x / dout / output");
+  if (xs < N || os < N || (bwd && ds < N)) return fail(B200NORM_ERR_ARG, "row stride smaller than N");
+  DeviceState* dev;
+  if (int rc = device_state(&dev)) return rc;
+  SoftmaxParams p;
+  p.x = x; p.dout = dout; p.out = out;
+  p.x_stride = xs; p.dout_stride = ds; p.out_stride = os;
+  p.M = M; p.N = static_cast<int>(N); p.V = static_cast<int>(N * es / 16); p.status = dev->status_dev;
+  const bool packets = (N * es) % 16 == 0 && aligned16(x, xs, es) && aligned16(out, os, es) &&
+                       (!bwd || aligned16(dout, ds, es));
+  const SoftmaxKernel* pk = nullptr;
+  if (packets)
+    for (int i = 0; i < k->n && pk == nullptr; ++i)
+      if (k->kernels[i].capacity() >= p.V) pk = &k->kernels[i];
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (pk != nullptr) {
+    const void* fn = pk->fn[log_softmax][bwd ? 1 : 0];
+    const int stages = bwd ? pk->stages_bwd : pk->stages_fwd;
+    const size_t smem = static_cast<size_t>(pk->warps_m) * stages * (bwd ? 2 : 1) * p.V * 16;
+    int occ;
+    if (int rc = occupancy(*dev, fn, pk->threads(), smem, &occ)) return rc;
+    const int64_t want = (M + pk->rows_per_cta() - 1) / pk->rows_per_cta();
+    const int grid = static_cast<int>(std::min<int64_t>(want, (int64_t)dev->sm_count * occ));
+    return launch(fn, dim3(grid), dim3(pk->threads()), smem, &p, s);
+  }
+  const void* fn = k->any[log_softmax][bwd ? 1 : 0];
+  int occ;
+  if (int rc = occupancy(*dev, fn, 256, 0, &occ)) return rc;
+  const int grid = static_cast<int>(std::min<int64_t>(M, (int64_t)dev->sm_count * occ));
+  return launch(fn, dim3(grid), dim3(256), 0, &p, s, false);
+}
+
 // ---------------------------------------------------------------------------------------
 // RMSNorm backward with built-in scratch (b200norm_rms_bwd_static): for hosts that plan their
 // device memory once and cannot hand over, or allocate, a workspace per call.
@@ -719,6 +767,17 @@ int b200norm_gelu_bwd(const void* x, int64_t x_row_stride, const void* dout, int
                       int64_t dx_row_stride, int64_t M, int64_t N, int approximate, int io_dtype, void* stream) {
   return act_impl(true, x, x_row_stride, dout, dout_row_stride, dx, dx_row_stride, M, N, approximate, io_dtype,
                   stream);
+}
+
+int b200norm_softmax_fwd(const void* x, int64_t x_row_stride, void* y, int64_t y_row_stride, int64_t M, int64_t N,
+                         int log_softmax, int io_dtype, void* stream) {
+  return softmax_impl(false, x, x_row_stride, nullptr, 0, y, y_row_stride, M, N, log_softmax, io_dtype, stream);
+}
+
+int b200norm_softmax_bwd(const void* y, int64_t y_row_stride, const void* dout, int64_t dout_row_stride, void* dx,
+                         int64_t dx_row_stride, int64_t M, int64_t N, int log_softmax, int io_dtype, void* stream) {
+  return softmax_impl(true, y, y_row_stride, dout, dout_row_stride, dx, dx_row_stride, M, N, log_softmax, io_dtype,
+                      stream);
 }
 
 int b200norm_rms_bwd_static(const void* x, int64_t x_row_stride, const void* dy, int64_t dy_row_stride,

@@ -33,6 +33,27 @@ struct DTypeKernels {
   const void* act_any[2];
 };
 
+// Softmax / LogSoftmax: one shape list per storage type; fn[log][bwd].
+struct SoftmaxKernel {
+  int ldgs, warps_m, warps_n;
+  int stages_fwd, stages_bwd;  // bulk-copy slots per row group (0: direct loads)
+  int lanes;                   // lanes of a warp per row (32, or fewer for short rows)
+  const void* fn[2][2];
+  int capacity() const { return ldgs * lanes * warps_n; }
+  int threads() const { return 32 * warps_m * warps_n; }
+  int rows_per_cta() const { return warps_m * (32 / lanes); }
+};
+struct SoftmaxTable {
+  int elem_size;
+  const SoftmaxKernel* kernels;  // ascending capacity
+  int n;
+  const void* any[2][2];  // any-alignment kernels, [log][bwd]
+};
+const SoftmaxTable* softmax_kernels_f32();
+const SoftmaxTable* softmax_kernels_f16();
+const SoftmaxTable* softmax_kernels_bf16();
+const SoftmaxTable* softmax_kernels_f64();
+
 // One table per (storage type, fused activation: 0 none, 1 GeLU erf, 2 GeLU tanh).
 #define B200NORM_DECLARE_TABLES(name)      \
   const DTypeKernels* kernels_##name##_act0(); \

@@ -1,0 +1,298 @@
+// Row-wise Softmax and LogSoftmax, forward and backward (TritonHub/Activations/softmax.py:11-62,
+// logsoftmax.py:11-68; Softmin is Softmax of -x, softmin.py:103).  Same skeleton as the norm
+// kernels -- a row in registers, one row reduction, rows staged through shared memory by bulk
+// asynchronous copies -- and the same roofline: 2 row passes forward, 3 backward, no parameters.
+//
+// Forward: each thread forms the maximum m_t of its elements and s_t = sum exp(x - m_t); the row
+// group merges the (m, s) pairs online, m = max(ma, mb), s = sa*exp(ma - m) + sb*exp(mb - m), in one
+// reduction.  Softmax then scales the exponentials it already holds: y = exp(x - m_t) * exp(m_t - m) / s
+// (softmax.py:19-22); LogSoftmax writes y = (x - m) - log s (logsoftmax.py:20-22).  fp32 throughout.
+// Backward reads the saved OUTPUT y: Softmax dx = y * (dout - sum(dout * y)) (softmax.py:57-59);
+// LogSoftmax dx = dout - exp(y) * sum(dout) (logsoftmax.py:63-65).
+#pragma once
+
+#include <math_constants.h>
+
+#include "norm_common.cuh"
+#include "norm_stage.cuh"
+
+namespace b200norm {
+
+struct SoftmaxParams {
+  const void* x;     // forward: input; backward: the saved output y
+  const void* dout;  // backward only
+  void* out;         // forward: y; backward: dx
+  int64_t x_stride, dout_stride, out_stride;  // elements
+  int64_t M;
+  int N;
+  int V;  // packets per row (packet kernels)
+  int* status;
+};
+
+// Online merge of (max, sum of exponentials relative to that max).
+__device__ __forceinline__ void maxsum_merge(float& m, float& s, float mb, float sb) {
+  // One of the two scale factors is always exp(0) = 1: a single exponential of -|ma - mb| serves.
+  // Two empty pairs (-inf, 0) give exp(NaN) * 0 on the scaled side, hence the guard.
+  const bool a_is_max = m >= mb;
+  const float d = a_is_max ? mb - m : m - mb;
+  const float e = (d == d) ? __expf(d) : 0.f;
+  const float big = a_is_max ? s : sb, small = a_is_max ? sb : s;
+  s = (m == mb) ? s + sb : fmaf(small, e, big);  // equal maxima: a commutative add on both sides
+  m = a_is_max ? m : mb;
+}
+
+template <int WARPS_N, int LANES>
+__device__ __forceinline__ void group_maxsum(float& m, float& s, float* scratch, int& phase, int warp_m, int warp_n,
+                                             int lane) {
+#pragma unroll
+  for (int o = LANES / 2; o > 0; o >>= 1) {
+    const float mb = __shfl_xor_sync(0xffffffffu, m, o);
+    const float sb = __shfl_xor_sync(0xffffffffu, s, o);
+    // The merge is symmetric down to the bits (both partners evaluate fma(smaller-side sum, e,
+    // larger-side sum)), so no lane ordering -- and no divergent branch -- is needed.
+    maxsum_merge(m, s, mb, sb);
+  }
+  if (WARPS_N > 1) {
+    float* buf = scratch + phase * (2 * WARPS_N);
+    if (lane == 0) {
+      buf[warp_n] = m;
+      buf[WARPS_N + warp_n] = s;
+    }
+    group_sync<WARPS_N>(warp_m);
+    m = buf[0];
+    s = buf[WARPS_N];
+#pragma unroll
+    for (int k = 1; k < WARPS_N; ++k) maxsum_merge(m, s, buf[k], buf[WARPS_N + k]);
+    phase ^= 1;
+  }
+}
+
+template <int LANES>
+__device__ __forceinline__ float lanes_add(float v) {
+#pragma unroll
+  for (int o = LANES / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// One kernel for both directions and both functions.  BWD: rows of y and dout are staged side by
+// side (two bulk copies per slot).  LANES < 32 (with WARPS_N == 1, STAGES == 0): short rows, 32 /
+// LANES of them per warp, loaded straight from global memory.
+template <typename T, int LDGS, int WARPS_M, int WARPS_N, int STAGES, int MINB, int LANES, bool LOG, bool BWD>
+__global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) softmax_kernel(const SoftmaxParams p) {
+  static_assert(LANES == 32 || (WARPS_N == 1 && STAGES == 0), "short rows: one warp, direct loads");
+  constexpr int VEC = Pack16<T>::kElems;
+  constexpr int TPR = WARPS_N * LANES;
+  constexpr int RPW = 32 / LANES;
+  constexpr int NBAR = STAGES > 0 ? WARPS_M * STAGES : 1;
+  constexpr int ROWS = BWD ? 2 : 1;  // rows per slot
+  extern __shared__ __align__(128) unsigned char dyn_smem[];
+  __shared__ float red_smem[WARPS_M][2 * 2 * WARPS_N];
+  __shared__ __align__(8) uint64_t full_bar[NBAR];
+  __shared__ int cta_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp_m = warp / WARPS_N, warp_n = warp % WARPS_N;
+  const int t = warp_n * 32 + lane % LANES, sub = lane / LANES;
+  int phase = 0;
+
+  const T* xb = static_cast<const T*>(p.x);
+  const T* gb = static_cast<const T*>(p.dout);
+  T* ob = static_cast<T*>(p.out);
+  const int64_t first = ((int64_t)blockIdx.x * WARPS_M + warp_m) * RPW;
+  const int64_t step = (int64_t)gridDim.x * WARPS_M * RPW;
+  const uint32_t row_bytes = static_cast<uint32_t>(p.V) * 16u;
+  unsigned char* slots = dyn_smem + (size_t)warp_m * STAGES * ROWS * row_bytes;
+  uint64_t* bars = full_bar + (STAGES > 0 ? warp_m * STAGES : 0);
+
+  auto fill = [&](int s, int64_t r) {
+    unsigned char* dst = slots + (size_t)s * ROWS * row_bytes;
+    mbar_expect_tx(&bars[s], ROWS * row_bytes);
+    bulk_load(dst, xb + r * p.x_stride, row_bytes, &bars[s]);
+    if (BWD) bulk_load(dst + row_bytes, gb + r * p.dout_stride, row_bytes, &bars[s]);
+  };
+
+  if (STAGES > 0) {
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < NBAR; ++i) mbar_init(&full_bar[i], 1);
+      cta_abort = 0;
+      mbar_init_fence();
+    }
+    __syncthreads();
+  }
+  grid_dependency_sync();
+  trigger_dependents();
+  if (STAGES > 0 && t == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      const int64_t r = first + s * step;
+      if (r < p.M) fill(s, r);
+    }
+  }
+  int slot = 0;
+  uint32_t parity = 0;
+
+  for (int64_t base = first; base < p.M; base += step) {
+    const int64_t row = base + sub;
+    const bool valid = row < p.M;
+    const int64_t r = valid ? row : 0;
+    // The row stays PACKED in registers and is unpacked where it is used: LogSoftmax needs x again
+    // after the reduction, and holding it as fp32 next to the exponentials would halve occupancy.
+    uint4 px[LDGS], pg[BWD ? LDGS : 1];
+    if (STAGES > 0) {
+      mbar_wait(&bars[slot], parity, &cta_abort, p.status);
+      const uint4* sx = reinterpret_cast<const uint4*>(slots + (size_t)slot * ROWS * row_bytes);
+      const uint4* sg = reinterpret_cast<const uint4*>(slots + (size_t)slot * ROWS * row_bytes + row_bytes);
+#pragma unroll
+      for (int j = 0; j < LDGS; ++j) {
+        const int v = j * TPR + t;
+        px[j] = make_uint4(0, 0, 0, 0);
+        if (BWD) pg[j] = make_uint4(0, 0, 0, 0);
+        if (v < p.V) {
+          px[j] = ld_shared16(sx + v);
+          if (BWD) pg[j] = ld_shared16(sg + v);
+        }
+      }
+    } else {
+      const uint4* xrow = reinterpret_cast<const uint4*>(xb + r * p.x_stride);
+      const uint4* grow = reinterpret_cast<const uint4*>(gb + r * p.dout_stride);
+#pragma unroll
+      for (int j = 0; j < LDGS; ++j) {
+        const int v = j * TPR + t;
+        px[j] = make_uint4(0, 0, 0, 0);
+        if (BWD) pg[j] = make_uint4(0, 0, 0, 0);
+        if (valid && v < p.V) {
+          px[j] = ld_stream(xrow + v);
+          if (BWD) pg[j] = ld_stream(grow + v);
+        }
+      }
+    }
+
+    float o[LDGS][VEC];
+    if (!BWD) {
+      float m = -CUDART_INF_F, s = 0.f;
+#pragma unroll
+      for (int j = 0; j < LDGS; ++j) {
+        if ((j * TPR + t) < p.V) {
+          float xf[VEC];
+          Pack16<T>::unpack(px[j], xf);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) m = fmaxf(m, xf[e]);
+        }
+      }
+      const float m_t = m;
+#pragma unroll
+      for (int j = 0; j < LDGS; ++j) {
+        const bool live = (j * TPR + t) < p.V;
+        float xf[VEC];
+        Pack16<T>::unpack(px[j], xf);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          const float ex = live ? __expf(xf[e] - m_t) : 0.f;
+          s += ex;
+          o[j][e] = ex;  // Softmax scales these below; LogSoftmax overwrites them
+        }
+      }
+      group_maxsum<WARPS_N, LANES>(m, s, red_smem[warp_m], phase, warp_m, warp_n, lane);
+      if (LOG) {
+        const float shift = m + __logf(s);  // y = (x - m) - log s
+#pragma unroll
+        for (int j = 0; j < LDGS; ++j) {
+          // keep the compiler from carrying the fp32 copy of x across the reduction
+          asm volatile("" : "+r"(px[j].x), "+r"(px[j].y), "+r"(px[j].z), "+r"(px[j].w));
+          float xf[VEC];
+          Pack16<T>::unpack(px[j], xf);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) o[j][e] = xf[e] - shift;
+        }
+      } else {
+        const float f = ((m_t == m) ? 1.f : __expf(m_t - m)) / s;  // exp(x - m) / s = exp(x - m_t) * f
+#pragma unroll
+        for (int j = 0; j < LDGS; ++j)
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) o[j][e] *= f;
+      }
+    } else {
+      float sacc[1] = {0.f};
+#pragma unroll
+      for (int j = 0; j < LDGS; ++j) {
+        float xf[VEC], gf[VEC];
+        Pack16<T>::unpack(px[j], xf);
+        Pack16<T>::unpack(pg[j], gf);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) sacc[0] += LOG ? gf[e] : gf[e] * xf[e];  // masked packets are zero
+      }
+      if (LANES == 32) {
+        group_sum<WARPS_N, 1>(sacc, red_smem[warp_m], phase, warp_m, warp_n, lane);
+      } else {
+        sacc[0] = lanes_add<LANES>(sacc[0]);
+      }
+      const float s = sacc[0];
+#pragma unroll
+      for (int j = 0; j < LDGS; ++j) {
+        float xf[VEC], gf[VEC];
+        Pack16<T>::unpack(px[j], xf);
+        Pack16<T>::unpack(pg[j], gf);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) o[j][e] = LOG ? (gf[e] - __expf(xf[e]) * s) : xf[e] * (gf[e] - s);
+      }
+    }
+    if (STAGES > 0) {
+      // every thread of the group has its packets in registers (the reduction above needed them)
+      if (t == 0) {
+        const int64_t rn = row + STAGES * step;
+        if (rn < p.M) fill(slot, rn);
+      }
+      if (++slot == STAGES) {
+        slot = 0;
+        parity ^= 1u;
+      }
+    }
+    uint4* orow = reinterpret_cast<uint4*>(ob + r * p.out_stride);
+#pragma unroll
+    for (int j = 0; j < LDGS; ++j) {
+      const int v = j * TPR + t;
+      if (valid && v < p.V) st_stream(orow + v, Pack16<T>::pack(o[j]));
+    }
+  }
+  if (STAGES > 0) {
+    if (t == 0 && cta_abort) drain_ring<STAGES>(bars, first < p.M ? (p.M - first + step - 1) / step : 0);
+  }
+}
+
+// Any alignment, any row length: one CTA per row, scalar accesses (re-reads hit L1/L2).
+template <typename T, bool LOG, bool BWD>
+__global__ void __launch_bounds__(256) softmax_any_kernel(const SoftmaxParams p) {
+  __shared__ float red[2 * 2 * 8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int phase = 0;
+  for (int64_t row = blockIdx.x; row < p.M; row += gridDim.x) {
+    const T* xrow = static_cast<const T*>(p.x) + row * p.x_stride;
+    T* orow = static_cast<T*>(p.out) + row * p.out_stride;
+    if (!BWD) {
+      float m = -CUDART_INF_F, s = 0.f;
+      for (int c = threadIdx.x; c < p.N; c += 256) m = fmaxf(m, to_f32(xrow[c]));
+      const float m_t = m;
+      for (int c = threadIdx.x; c < p.N; c += 256) s += __expf(to_f32(xrow[c]) - m_t);
+      group_maxsum<8, 32>(m, s, red, phase, -1, warp, lane);
+      const float shift = m + __logf(s);
+      for (int c = threadIdx.x; c < p.N; c += 256) {
+        const float xv = to_f32(xrow[c]);
+        orow[c] = from_f32<T>(LOG ? xv - shift : __expf(xv - m) / s);
+      }
+    } else {
+      const T* grow = static_cast<const T*>(p.dout) + row * p.dout_stride;
+      float sacc[1] = {0.f};
+      for (int c = threadIdx.x; c < p.N; c += 256) {
+        const float g = to_f32(grow[c]);
+        sacc[0] += LOG ? g : g * to_f32(xrow[c]);
+      }
+      group_sum<8, 1>(sacc, red, phase, -1, warp, lane);
+      for (int c = threadIdx.x; c < p.N; c += 256) {
+        const float y = to_f32(xrow[c]), g = to_f32(grow[c]);
+        orow[c] = from_f32<T>(LOG ? g - __expf(y) * sacc[0] : y * (g - sacc[0]));
+      }
+    }
+  }
+}
+
+}  // namespace b200norm
