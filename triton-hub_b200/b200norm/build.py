@@ -11,6 +11,7 @@ import os
 import shutil
 import subprocess
 import sys
+import threading
 from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
@@ -19,6 +20,8 @@ CSRC = PKG_DIR.parent / "csrc"
 INCLUDE = PKG_DIR.parent.parent / "include"
 BUILD_DIR = CSRC / "build"
 LIB_PATH = PKG_DIR / "libb200norm.so"
+
+_RETRY_LOCK = threading.Lock()
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -55,6 +58,10 @@ def _compile(src: Path, verbose: bool, ptxas_info: bool) -> Path:
     if verbose:
         print(" ".join(cmd), flush=True)
     res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0 and "error" not in res.stderr.lower():
+        # the compiler itself died (several large translation units in parallel): once more, alone
+        with _RETRY_LOCK:
+            res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"nvcc failed on {src.name}:\n{res.stdout}\n{res.stderr}")
     if ptxas_info:
@@ -69,7 +76,7 @@ def build_library(verbose: bool = False, force: bool = False, ptxas_info: bool =
         for o in BUILD_DIR.glob("*.o"):
             o.unlink()
     srcs = _sources()
-    with ThreadPoolExecutor(max_workers=min(len(srcs), os.cpu_count() or 4)) as pool:
+    with ThreadPoolExecutor(max_workers=min(len(srcs), max(2, (os.cpu_count() or 4) - 2))) as pool:
         objs = list(pool.map(lambda s: _compile(s, verbose, ptxas_info), srcs))
     if LIB_PATH.exists() and all(LIB_PATH.stat().st_mtime >= o.stat().st_mtime for o in objs):
         return LIB_PATH

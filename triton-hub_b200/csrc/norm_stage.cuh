@@ -75,11 +75,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 // rows over STAGES slots) a bounded chance to land before the CTA's shared memory is released.
 template <int STAGES>
 __device__ __forceinline__ void drain_ring(uint64_t* bars, int64_t count) {
+  constexpr int kSlots = STAGES > 0 ? STAGES : 1;  // instantiated (never called) with STAGES == 0
   const unsigned long long t0 = global_ns();
 #pragma unroll
   for (int s = 0; s < STAGES; ++s) {
     if (count <= s) continue;
-    const int64_t fills = (count - s + STAGES - 1) / STAGES;
+    const int64_t fills = (count - s + kSlots - 1) / kSlots;
     const uint32_t parity = static_cast<uint32_t>((fills - 1) & 1);
     while (!mbar_try_wait(&bars[s], parity)) {
       if (global_ns() - t0 > 10000000ull) return;  // 10 ms for the whole ring

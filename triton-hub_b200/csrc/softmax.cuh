@@ -197,8 +197,6 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) softmax_kernel(co
         const float shift = m + __logf(s);  // y = (x - m) - log s
 #pragma unroll
         for (int j = 0; j < LDGS; ++j) {
-          // keep the compiler from carrying the fp32 copy of x across the reduction
-          asm volatile("" : "+r"(px[j].x), "+r"(px[j].y), "+r"(px[j].z), "+r"(px[j].w));
           float xf[VEC];
           Pack16<T>::unpack(px[j], xf);
 #pragma unroll
