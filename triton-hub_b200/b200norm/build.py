@@ -52,7 +52,8 @@ def _compile(src: Path, verbose: bool, ptxas_info: bool) -> Path:
     newest = max(src.stat().st_mtime, _headers_mtime())
     if obj.exists() and obj.stat().st_mtime >= newest:
         return obj
-    cmd = [_nvcc(), *NVCC_FLAGS, f"-I{INCLUDE}", f"-I{CSRC}", "-c", str(src), "-o", str(obj)]
+    extra = os.environ.get("B200NORM_NVCC_EXTRA", "").split()  # e.g. -DB200NORM_SOFTMAX_CANDIDATES (tuning builds)
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra, f"-I{INCLUDE}", f"-I{CSRC}", "-c", str(src), "-o", str(obj)]
     if ptxas_info:
         cmd[1:1] = ["-Xptxas", "-v"]
     if verbose:

@@ -14,8 +14,8 @@ enum : int { kActNone = 0, kActGeluErf = 1, kActGeluTanh = 2 };
 // = NaN once exp(2u) overflows (x > ~10 in fp32); this form saturates to 1 instead and agrees
 // with it wherever the reference is finite.
 __device__ __forceinline__ float tanh_via_exp(float u) {
-  const float e = __expf(2.f * u);
-  return 1.f - __fdividef(2.f, e + 1.f);
+  const float e = ex2_fast(u * (2.f * kLog2e));
+  return fmaf(-2.f, rcp_fast(e + 1.f), 1.f);  // e = inf gives 1
 }
 
 // erf(s) for s = x / sqrt(2), from e = exp(-s*s) which the caller also needs for the Gaussian density.
@@ -23,7 +23,7 @@ __device__ __forceinline__ float tanh_via_exp(float u) {
 // whole line, one reciprocal, five FMAs -- a third of the instructions of the library erff, which
 // matters because these kernels are otherwise limited by HBM, not by arithmetic.
 __device__ __forceinline__ float erf_from_exp(float s, float e) {
-  const float t = __fdividef(1.f, fmaf(0.3275911f, fabsf(s), 1.f));
+  const float t = rcp_fast(fmaf(0.3275911f, fabsf(s), 1.f));
   const float poly =
       t * (0.254829592f + t * (-0.284496736f + t * (1.421413741f + t * (-1.453152027f + t * 1.061405429f))));
   return copysignf(1.f - poly * e, s);
@@ -33,7 +33,7 @@ template <int ACT>
 __device__ __forceinline__ float act_fwd(float x) {
   if (ACT == kActGeluErf) {
     const float s = x * 0.70710678118654752f;
-    return 0.5f * x * (1.f + erf_from_exp(s, __expf(-s * s)));  // gelu.py:27
+    return 0.5f * x * (1.f + erf_from_exp(s, ex2_fast(x * x * (-0.5f * kLog2e))));  // gelu.py:27
   } else if (ACT == kActGeluTanh) {
     const float inner = 0.79788456080286536f * (x + 0.044715f * x * x * x);  // gelu.py:22
     return 0.5f * x * (1.f + tanh_via_exp(inner));                           // gelu.py:25
@@ -46,7 +46,7 @@ template <int ACT>
 __device__ __forceinline__ float act_grad(float x) {
   if (ACT == kActGeluErf) {
     const float s = x * 0.70710678118654752f;
-    const float e = __expf(-s * s);                                        // exp(-x^2 / 2), used twice
+    const float e = ex2_fast(x * x * (-0.5f * kLog2e));                    // exp(-x^2 / 2), used twice
     const float cdf = 0.5f * (1.f + erf_from_exp(s, e));                   // gelu.py:76
     const float pdf = e * 0.39894228040143268f;                            // gelu.py:77
     return cdf + x * pdf;                                                  // gelu.py:78

@@ -62,9 +62,8 @@ struct BwdParams {
 // rank order, so they hold identical sums.  A "unit" below is the CTA (CL == 1) or the pair.
 //
 // ACT != 0: the incoming gradient is that of act(y), not of y.  y = xhat*w + b is rebuilt from the
-// row (the forward did not store it), the gradient is multiplied by act'(y) and repacked in the
-// storage type -- the precision a separate activation-backward kernel would have written it with
-// -- and the rest of the kernel runs unchanged on it.
+// row (the forward did not store it) inside pass 1 and the gradient is multiplied by act'(y);
+// the rest of the kernel runs unchanged on it.
 template <typename T, int LDGS, int WARPS_M, int WARPS_N, bool PREFETCH, int STAGES, bool KEEP, int MINB, int CL,
           int ACT, bool RMS>
 __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(const BwdParams p) {
@@ -197,25 +196,6 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
       }
     }
 
-    if (ACT != kActNone) {
-      // dy = dz * act'(y), y rebuilt from the row; repacked in place of dz.
-#pragma unroll
-      for (int j = 0; j < LDGS; ++j) {
-        const int v = j * TPR + t;
-        if (v < Vl) {
-          float xf[VEC], gf[VEC];
-          Pack16<T>::unpack(xv[j], xf);
-          Pack16<T>::unpack(gv[j], gf);
-#pragma unroll
-          for (int e = 0; e < VEC; ++e) {
-            const float y = (xf[e] - mu) * rs * w_s[v * VEC + e] + b_s[v * VEC + e];
-            gf[e] *= act_grad<ACT>(y);
-          }
-          gv[j] = Pack16<T>::pack(gf);
-        }
-      }
-    }
-
     // Pass 1: dweight / dbias sums and the two row sums (layernorm.py:132-138).
     float s[NV];
 #pragma unroll
@@ -229,6 +209,20 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
         float xf[VEC], gf[VEC];
         Pack16<T>::unpack(xv[j], xf);
         Pack16<T>::unpack(gv[j], gf);
+        if (ACT != kActNone) {
+          // dy = dz * act'(y) with y = xhat*w + b rebuilt from the row.  When pass 2 reads the packed
+          // row again, dy replaces dz there, rounded to the storage type as a separate activation
+          // backward would have stored it; the kept form carries it on in fp32.
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) {
+            const float y = fmaf((xf[e] - mu) * rs, w_s[v * VEC + e], b_s[v * VEC + e]);
+            gf[e] *= act_grad<ACT>(y);
+          }
+          if (!KEEP) {
+            gv[j] = Pack16<T>::pack(gf);
+            Pack16<T>::unpack(gv[j], gf);
+          }
+        }
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
           const float xh = (xf[e] - mu) * rs;
@@ -244,7 +238,9 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
         }
       }
     }
-    group_sum<WARPS_N, NV>(s, red_smem[warp_m], phase, warp_m, warp_n, lane);
+    // With a single row group its barrier is the CTA's barrier 0; several groups keep 1, 2, ... because
+    // a group that has finished its rows waits on barrier 0 (the final sum) while the others still loop.
+    group_sum<WARPS_N, NV, (WARPS_M == 1 ? 0 : 1)>(s, red_smem[warp_m], phase, warp_m, warp_n, lane);
     if (CL > 1) {
       // Swap this half's sums with the partner's and add them in rank order.
       if (threadIdx.x == 0) {

@@ -94,6 +94,20 @@ struct Pack16<double> {
   }
 };
 
+// 2^x and 1/x on the special-function unit, one instruction each (denormal results and inputs
+// flush to zero; the callers' arguments keep far from both).
+constexpr float kLog2e = 1.4426950408889634f;
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_fast(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // Scalar conversions for the any-alignment kernels.
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
@@ -189,11 +203,13 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // Barrier over the WARPS_N warps that share a row.  Barrier 0 is __syncthreads; row group m
-// uses hardware barrier m+1 (at most 15 row groups per CTA).
-template <int WARPS_N>
+// uses hardware barrier m + FIRST (at most 15 row groups per CTA).  A kernel that never calls
+// __syncthreads once its row groups run apart may pass FIRST = 0: the SM has 16 barriers, so one
+// barrier less per CTA is up to twice as many small CTAs per SM.
+template <int WARPS_N, int FIRST = 1>
 __device__ __forceinline__ void group_sync(int warp_m) {
   if (WARPS_N > 1) {
-    asm volatile("bar.sync %0, %1;" ::"r"(warp_m + 1), "r"(WARPS_N * 32) : "memory");
+    asm volatile("bar.sync %0, %1;" ::"r"(warp_m + FIRST), "r"(WARPS_N * 32) : "memory");
   }
 }
 
@@ -203,7 +219,7 @@ __device__ __forceinline__ void group_sync(int warp_m) {
 // warp cannot overwrite a half before every warp has read it, because a full barrier lies
 // between.  The cross-warp add runs in warp order in every thread: deterministic and
 // identical across the group.
-template <int WARPS_N, int NV>
+template <int WARPS_N, int NV, int FIRST = 1>
 __device__ __forceinline__ void group_sum(float (&v)[NV], float* scratch, int& phase, int warp_m, int warp_n,
                                           int lane) {
 #pragma unroll
@@ -214,7 +230,7 @@ __device__ __forceinline__ void group_sum(float (&v)[NV], float* scratch, int& p
 #pragma unroll
       for (int i = 0; i < NV; ++i) buf[i * WARPS_N + warp_n] = v[i];
     }
-    group_sync<WARPS_N>(warp_m);
+    group_sync<WARPS_N, FIRST>(warp_m);
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       float s = 0.f;
@@ -235,7 +251,7 @@ __device__ __forceinline__ void group_sum(float (&v)[NV], float* scratch, int& p
 // butterfly partners compute the same bits.  The warp pairs go through shared memory and every
 // thread folds them in warp order: the whole row group ends with identical statistics.
 // `n` is the element count per thread on entry and per row group on return.
-template <int WARPS_N>
+template <int WARPS_N, int FIRST = 1>
 __device__ __forceinline__ void group_moments(float& n, float& mean, float& m2, float* scratch, int& phase,
                                               int warp_m, int warp_n, int lane) {
   float half = 0.5f * n;  // na * nb / (na + nb) for equal counts
@@ -255,7 +271,7 @@ __device__ __forceinline__ void group_moments(float& n, float& mean, float& m2, 
       buf[warp_n] = mean;
       buf[WARPS_N + warp_n] = m2;
     }
-    group_sync<WARPS_N>(warp_m);
+    group_sync<WARPS_N, FIRST>(warp_m);
     const float nw = n;  // elements per warp
     mean = buf[0];
     m2 = buf[WARPS_N];

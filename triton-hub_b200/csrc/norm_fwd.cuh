@@ -182,7 +182,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
             q[0] += d * d;
           }
         }
-        group_moments<WARPS_N>(cnt, mean, q[0], red_smem[warp_m], phase, warp_m, warp_n, lane);
+        group_moments<WARPS_N, 0>(cnt, mean, q[0], red_smem[warp_m], phase, warp_m, warp_n, lane);
         if (CL > 1) {  // merge the two halves (equal counts), rank 0's first
           const float mine[2] = {mean, q[0]};
           float theirs[2];
@@ -196,7 +196,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
       } else {
         // Ragged rows (threads hold different element counts): the reference's two passes,
         // mean first, then the centred sum of squares (layernorm.py:32-35).
-        group_sum<WARPS_N, 1>(s, red_smem[warp_m], phase, warp_m, warp_n, lane);
+        group_sum<WARPS_N, 1, 0>(s, red_smem[warp_m], phase, warp_m, warp_n, lane);
         if (CL > 1) {
           const float mine[2] = {s[0], 0.f};
           float theirs[2];
@@ -210,7 +210,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
       for (int j = 0; j < LDGS; ++j)
 #pragma unroll
         for (int e = 0; e < VEC; ++e) q[0] += xf[j][e] * xf[j][e];
-      group_sum<WARPS_N, 1>(q, red_smem[warp_m], phase, warp_m, warp_n, lane);
+      group_sum<WARPS_N, 1, 0>(q, red_smem[warp_m], phase, warp_m, warp_n, lane);
       if (CL > 1) {
         const float mine[2] = {q[0], 0.f};
         float theirs[2];
@@ -242,7 +242,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
           q[0] += d * d;
         }
       }
-      group_sum<WARPS_N, 1>(q, red_smem[warp_m], phase, warp_m, warp_n, lane);
+      group_sum<WARPS_N, 1, 0>(q, red_smem[warp_m], phase, warp_m, warp_n, lane);
       if (CL > 1) {
         const float mine[2] = {q[0], 0.f};
         float theirs[2];

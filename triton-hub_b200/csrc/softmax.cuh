@@ -16,6 +16,12 @@
 #include "norm_common.cuh"
 #include "norm_stage.cuh"
 
+// 16-bit Softmax forward: 1 keeps the exponentials of pass 1 in registers and scales them, 0
+// recomputes them from the packed row (fewer registers, one more exponential per element).
+#ifndef B200NORM_SOFTMAX_HOLD16
+#define B200NORM_SOFTMAX_HOLD16 1
+#endif
+
 namespace b200norm {
 
 struct SoftmaxParams {
@@ -29,28 +35,53 @@ struct SoftmaxParams {
   int* status;
 };
 
-// Online merge of (max, sum of exponentials relative to that max).
+// Maximum over the warp in one instruction (sm_100a: redux.sync on fp32).
+__device__ __forceinline__ float warp_max(float v) {
+  float r;
+  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
+}
+
+// s counts exponentials relative to m; re-base it on M >= m.  m == M covers the empty pair
+// (-inf, 0), whose difference would be NaN.
+__device__ __forceinline__ float rebase(float s, float m, float M) {
+  return (m == M) ? s : s * ex2_fast((m - M) * kLog2e);
+}
+
+// Online merge of (max, sum of exponentials relative to that max), for the short-row kernels.
 __device__ __forceinline__ void maxsum_merge(float& m, float& s, float mb, float sb) {
   // One of the two scale factors is always exp(0) = 1: a single exponential of -|ma - mb| serves.
   // Two empty pairs (-inf, 0) give exp(NaN) * 0 on the scaled side, hence the guard.
   const bool a_is_max = m >= mb;
   const float d = a_is_max ? mb - m : m - mb;
-  const float e = (d == d) ? __expf(d) : 0.f;
+  const float e = (d == d) ? ex2_fast(d * kLog2e) : 0.f;
   const float big = a_is_max ? s : sb, small = a_is_max ? sb : s;
   s = (m == mb) ? s + sb : fmaf(small, e, big);  // equal maxima: a commutative add on both sides
   m = a_is_max ? m : mb;
 }
 
+// (max, sum) of a row from per-thread pairs; every thread of the group gets the result.  The
+// dependent chain is short on purpose -- a row waits on it with nothing else to do: the maximum
+// first (one redux per warp), one re-basing exponential per thread, then a plain butterfly sum;
+// across warps the same again with lane k holding warp k's pair.  All lanes add in the same
+// order, so the result is identical across the group and from run to run.
 template <int WARPS_N, int LANES>
 __device__ __forceinline__ void group_maxsum(float& m, float& s, float* scratch, int& phase, int warp_m, int warp_n,
                                              int lane) {
+  static_assert((WARPS_N & (WARPS_N - 1)) == 0 && WARPS_N <= 32, "lane k reads warp k's pair");
+  if (LANES == 32) {
+    const float mw = warp_max(m);
+    s = warp_sum(rebase(s, m, mw));
+    m = mw;
+  } else {
 #pragma unroll
-  for (int o = LANES / 2; o > 0; o >>= 1) {
-    const float mb = __shfl_xor_sync(0xffffffffu, m, o);
-    const float sb = __shfl_xor_sync(0xffffffffu, s, o);
-    // The merge is symmetric down to the bits (both partners evaluate fma(smaller-side sum, e,
-    // larger-side sum)), so no lane ordering -- and no divergent branch -- is needed.
-    maxsum_merge(m, s, mb, sb);
+    for (int o = LANES / 2; o > 0; o >>= 1) {
+      const float mb = __shfl_xor_sync(0xffffffffu, m, o);
+      const float sb = __shfl_xor_sync(0xffffffffu, s, o);
+      // symmetric down to the bits (both partners evaluate fma(smaller-side sum, e, larger-side
+      // sum)), so no lane ordering and no divergent branch
+      maxsum_merge(m, s, mb, sb);
+    }
   }
   if (WARPS_N > 1) {
     float* buf = scratch + phase * (2 * WARPS_N);
@@ -58,14 +89,55 @@ __device__ __forceinline__ void group_maxsum(float& m, float& s, float* scratch,
       buf[warp_n] = m;
       buf[WARPS_N + warp_n] = s;
     }
-    group_sync<WARPS_N>(warp_m);
-    m = buf[0];
-    s = buf[WARPS_N];
+    group_sync<WARPS_N, 0>(warp_m);  // this file's kernels use no CTA-wide barrier after set-up
+    const int k = lane & (WARPS_N - 1);
+    const float mk = buf[k];
+    float sk = buf[WARPS_N + k];
+    m = warp_max(mk);
+    sk = rebase(sk, mk, m);
 #pragma unroll
-    for (int k = 1; k < WARPS_N; ++k) maxsum_merge(m, s, buf[k], buf[WARPS_N + k]);
+    for (int o = WARPS_N / 2; o > 0; o >>= 1) sk += __shfl_xor_sync(0xffffffffu, sk, o);
+    s = sk;
     phase ^= 1;
   }
 }
+
+// Maximum of a packet's elements without leaving the packed form (16-bit types: four paired
+// maxima per packet instead of eight conversions and eight scalar maxima).
+template <typename T>
+struct PackedMax {
+  static constexpr bool kPacked = false;
+};
+template <>
+struct PackedMax<__half> {
+  static constexpr bool kPacked = true;
+  static constexpr uint32_t kNegInf = 0xfc00fc00u;
+  __device__ __forceinline__ static uint32_t max2(uint32_t a, uint32_t b) {
+    const __half2 r = __hmax2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+  }
+  __device__ __forceinline__ static float finish(uint32_t a) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&a));
+    return fmaxf(f.x, f.y);
+  }
+};
+template <>
+struct PackedMax<__nv_bfloat16> {
+  static constexpr bool kPacked = true;
+  static constexpr uint32_t kNegInf = 0xff80ff80u;
+  __device__ __forceinline__ static uint32_t max2(uint32_t a, uint32_t b) {
+    const __nv_bfloat162 r =
+        __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+  }
+  __device__ __forceinline__ static float finish(uint32_t a) {
+    return fmaxf(__uint_as_float(a << 16), __uint_as_float(a & 0xffff0000u));
+  }
+};
+
+// Makes the compiler forget what it knows about a packet, so that a later unpack is redone from
+// the packed registers instead of keeping every fp32 copy alive across the row reduction.
+__device__ __forceinline__ void forget(uint4& v) { asm volatile("" : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)); }
 
 template <int LANES>
 __device__ __forceinline__ float lanes_add(float v) {
@@ -167,19 +239,36 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) softmax_kernel(co
       }
     }
 
-    float o[LDGS][VEC];
+    // Pass 1: the row reduction.  Forward: per-thread maximum m_t and s = sum exp(x - m_t), merged
+    // over the group; backward: sum(dout) or sum(dout * y).
+    constexpr bool HOLD = !BWD && !LOG && (sizeof(T) >= 4 || B200NORM_SOFTMAX_HOLD16);
+    float held[HOLD ? LDGS : 1][VEC];  // Softmax forward: the exponentials, scaled in pass 2
+    float m_t = 0.f, m_row = 0.f, s_row = 0.f;
     if (!BWD) {
-      float m = -CUDART_INF_F, s = 0.f;
+      float m = -CUDART_INF_F;
+      if constexpr (PackedMax<T>::kPacked) {
+        uint32_t acc = PackedMax<T>::kNegInf;
 #pragma unroll
-      for (int j = 0; j < LDGS; ++j) {
-        if ((j * TPR + t) < p.V) {
-          float xf[VEC];
-          Pack16<T>::unpack(px[j], xf);
+        for (int j = 0; j < LDGS; ++j) {
+          if ((j * TPR + t) < p.V) {
+            using PM = PackedMax<T>;
+            acc = PM::max2(acc, PM::max2(PM::max2(px[j].x, px[j].y), PM::max2(px[j].z, px[j].w)));
+          }
+        }
+        m = PackedMax<T>::finish(acc);
+      } else {
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) m = fmaxf(m, xf[e]);
+        for (int j = 0; j < LDGS; ++j) {
+          if ((j * TPR + t) < p.V) {
+            float xf[VEC];
+            Pack16<T>::unpack(px[j], xf);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) m = fmaxf(m, xf[e]);
+          }
         }
       }
-      const float m_t = m;
+      m_t = m;
+      float s = 0.f;
 #pragma unroll
       for (int j = 0; j < LDGS; ++j) {
         const bool live = (j * TPR + t) < p.V;
@@ -187,28 +276,14 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) softmax_kernel(co
         Pack16<T>::unpack(px[j], xf);
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
-          const float ex = live ? __expf(xf[e] - m_t) : 0.f;
+          const float ex = live ? ex2_fast((xf[e] - m_t) * kLog2e) : 0.f;
           s += ex;
-          o[j][e] = ex;  // Softmax scales these below; LogSoftmax overwrites them
+          if (HOLD) held[j][e] = ex;
         }
       }
       group_maxsum<WARPS_N, LANES>(m, s, red_smem[warp_m], phase, warp_m, warp_n, lane);
-      if (LOG) {
-        const float shift = m + __logf(s);  // y = (x - m) - log s
-#pragma unroll
-        for (int j = 0; j < LDGS; ++j) {
-          float xf[VEC];
-          Pack16<T>::unpack(px[j], xf);
-#pragma unroll
-          for (int e = 0; e < VEC; ++e) o[j][e] = xf[e] - shift;
-        }
-      } else {
-        const float f = ((m_t == m) ? 1.f : __expf(m_t - m)) / s;  // exp(x - m) / s = exp(x - m_t) * f
-#pragma unroll
-        for (int j = 0; j < LDGS; ++j)
-#pragma unroll
-          for (int e = 0; e < VEC; ++e) o[j][e] *= f;
-      }
+      m_row = m;
+      s_row = s;
     } else {
       float sacc[1] = {0.f};
 #pragma unroll
@@ -220,19 +295,11 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) softmax_kernel(co
         for (int e = 0; e < VEC; ++e) sacc[0] += LOG ? gf[e] : gf[e] * xf[e];  // masked packets are zero
       }
       if (LANES == 32) {
-        group_sum<WARPS_N, 1>(sacc, red_smem[warp_m], phase, warp_m, warp_n, lane);
+        group_sum<WARPS_N, 1, 0>(sacc, red_smem[warp_m], phase, warp_m, warp_n, lane);
       } else {
         sacc[0] = lanes_add<LANES>(sacc[0]);
       }
-      const float s = sacc[0];
-#pragma unroll
-      for (int j = 0; j < LDGS; ++j) {
-        float xf[VEC], gf[VEC];
-        Pack16<T>::unpack(px[j], xf);
-        Pack16<T>::unpack(pg[j], gf);
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) o[j][e] = LOG ? (gf[e] - __expf(xf[e]) * s) : xf[e] * (gf[e] - s);
-      }
+      s_row = sacc[0];
     }
     if (STAGES > 0) {
       // every thread of the group has its packets in registers (the reduction above needed them)
@@ -245,11 +312,42 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) softmax_kernel(co
         parity ^= 1u;
       }
     }
+
+    // Pass 2: packet by packet from the packed registers, straight to the store.
+    float f_scale = 0.f, shift = 0.f;
+    if (!BWD) {
+      if (LOG) {
+        shift = m_row + __logf(s_row);  // y = (x - m) - log s
+      } else if (HOLD) {
+        f_scale = rebase(1.f, m_t, m_row) / s_row;  // exp(x - m) / s = exp(x - m_t) * f
+      } else {
+        shift = __log2f(s_row);  // y = 2^((x - m) * log2(e) - log2(s))
+      }
+    }
     uint4* orow = reinterpret_cast<uint4*>(ob + r * p.out_stride);
 #pragma unroll
     for (int j = 0; j < LDGS; ++j) {
+      float xf[VEC], gf[VEC], o[VEC];
+      if (sizeof(T) < 4) {
+        forget(px[j]);
+        if (BWD) forget(pg[j]);
+      }
+      Pack16<T>::unpack(px[j], xf);
+      if (BWD) Pack16<T>::unpack(pg[j], gf);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        if (BWD) {
+          o[e] = LOG ? (gf[e] - ex2_fast(xf[e] * kLog2e) * s_row) : xf[e] * (gf[e] - s_row);
+        } else if (LOG) {
+          o[e] = xf[e] - shift;
+        } else if (HOLD) {
+          o[e] = held[j][e] * f_scale;
+        } else {
+          o[e] = ex2_fast(fmaf(xf[e] - m_row, kLog2e, -shift));
+        }
+      }
       const int v = j * TPR + t;
-      if (valid && v < p.V) st_stream(orow + v, Pack16<T>::pack(o[j]));
+      if (valid && v < p.V) st_stream(orow + v, Pack16<T>::pack(o));
     }
   }
   if (STAGES > 0) {
@@ -271,7 +369,7 @@ __global__ void __launch_bounds__(256) softmax_any_kernel(const SoftmaxParams p)
       for (int c = threadIdx.x; c < p.N; c += 256) m = fmaxf(m, to_f32(xrow[c]));
       const float m_t = m;
       for (int c = threadIdx.x; c < p.N; c += 256) s += __expf(to_f32(xrow[c]) - m_t);
-      group_maxsum<8, 32>(m, s, red, phase, -1, warp, lane);
+      group_maxsum<8, 32>(m, s, red, phase, 0, warp, lane);
       const float shift = m + __logf(s);
       for (int c = threadIdx.x; c < p.N; c += 256) {
         const float xv = to_f32(xrow[c]);
@@ -284,7 +382,7 @@ __global__ void __launch_bounds__(256) softmax_any_kernel(const SoftmaxParams p)
         const float g = to_f32(grow[c]);
         sacc[0] += LOG ? g : g * to_f32(xrow[c]);
       }
-      group_sum<8, 1>(sacc, red, phase, -1, warp, lane);
+      group_sum<8, 1, 0>(sacc, red, phase, 0, warp, lane);
       for (int c = threadIdx.x; c < p.N; c += 256) {
         const float y = to_f32(xrow[c]), g = to_f32(grow[c]);
         orow[c] = from_f32<T>(LOG ? g - __expf(y) * sacc[0] : y * (g - sacc[0]));
