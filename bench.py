@@ -439,6 +439,7 @@ def run_gpu(args):
         "eager_ms_per_step": round(eager_ms, 5),
         "rows_per_s": round(total_rows / (ms_per_step * 1e-3), 1),
         "frac_of_peak": round(value / world / peak, 4),
+        "frac_of_nominal_8000": round(value / world / 8000.0, 4),
         "peak_gbs_per_gpu": peak,
         "peak_source": peak_src,
         "roofline": {
@@ -466,12 +467,77 @@ def run_gpu(args):
     }
     if e2e is not None:
         line["e2e"] = e2e
+    if world == 1 and approx is None and not args.no_torch:
+        line["gpu_baseline"] = torch_gpu_baseline(wl, x, dy, w, b, eps, fwd_bytes + bwd_bytes)
+        if not args.no_triton_ref:
+            line["reference_triton_gpu"] = reference_triton_gpu(wl, rows, fwd_bytes + bwd_bytes)
     if rank == 0 and world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(wl, budget_s=args.cpu_seconds)
     if world > 1:
         dist.destroy_process_group()
     if rank == 0:
         print(json.dumps(line), flush=True)
+
+
+def torch_gpu_baseline(wl, x, dy, w, b, eps, step_bytes, reps=10):
+    """The same fwd+bwd through torch's own CUDA kernels (F.layer_norm / F.rms_norm with autograd) on
+    the same device-resident tensors: the library baseline on this box, reported beside `value`."""
+    import torch.nn.functional as F
+    N = x.shape[-1]
+    try:
+        xr = x.detach().requires_grad_(True)
+        wr = w.detach().clone().requires_grad_(True)
+        br = b.detach().clone().requires_grad_(True) if (wl["op"] == "ln" and b is not None) else None
+
+        def one():
+            xr.grad = None
+            wr.grad = None
+            if br is not None:
+                br.grad = None
+            y = F.layer_norm(xr, (N,), wr, br, eps) if wl["op"] == "ln" else F.rms_norm(xr, (N,), wr, eps)
+            y.backward(dy)
+
+        for _ in range(3):
+            one()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        s.record()
+        for _ in range(reps):
+            one()
+        e.record()
+        torch.cuda.synchronize()
+        ms = s.elapsed_time(e) / reps
+        xr.grad = None
+        return {"kind": "torch " + torch.__version__ + (" F.layer_norm" if wl["op"] == "ln" else " F.rms_norm")
+                        + " + autograd, CUDA, eager", "value": round(step_bytes / (ms * 1e-3) / 1e9, 1),
+                "unit": "GB/s", "ms_per_step": round(ms, 5), "steps": reps}
+    except Exception as exc:  # an out-of-memory error here must not lose the measurement above
+        torch.cuda.empty_cache()
+        return {"kind": "torch CUDA", "unavailable": f"{type(exc).__name__}: {str(exc)[:120]}"}
+
+
+def reference_triton_gpu(wl, rows, step_bytes, reps=10, timeout_s=420):
+    """The reference's own Triton kernels on this GPU (its modules, unmodified, from baseline/_ref),
+    timed in a child process by baseline/time_reference_gpu.py: the kernels this library replaces."""
+    import subprocess
+    script = ROOT / "baseline" / "time_reference_gpu.py"
+    cmd = [sys.executable, str(script), wl["op"], wl["dtype"], str(rows), str(wl["N"]), str(wl["eps"]),
+           str(wl["mu"]), str(wl["sigma"]), str(reps)]
+    kind = "TritonHub 1.1.1 " + ("LayerNorm" if wl["op"] == "ln" else "RMSNorm") + " module (Triton JIT, autotuned), CUDA, eager"
+    try:
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout_s)
+        last = [ln for ln in res.stdout.splitlines() if ln.startswith("{")]
+        if res.returncode != 0 or not last:
+            tail = (res.stderr.strip().splitlines() or ["no output"])[-1]
+            return {"kind": kind, "unavailable": f"exit {res.returncode}: {tail[:160]}"}
+        out = json.loads(last[-1])
+        if "unavailable" in out:
+            return {"kind": kind, **out}
+        ms = out["ms_per_step"]
+        return {"kind": kind + f" (triton {out['triton']})", "value": round(step_bytes / (ms * 1e-3) / 1e9, 1),
+                "unit": "GB/s", "ms_per_step": round(ms, 5), "steps": out["steps"]}
+    except subprocess.TimeoutExpired:
+        return {"kind": kind, "unavailable": f"no result within {timeout_s} s"}
 
 
 def run_e2e(wl, x, dy, w, b, rows, world, device, args):
@@ -643,6 +709,9 @@ def main():
     ap.add_argument("--unfused", action="store_true", help="with --act: run norm and GeLU as separate kernels")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-torch", action="store_true", help="skip the torch CUDA baseline (gpu_baseline)")
+    ap.add_argument("--no-triton-ref", action="store_true",
+                    help="skip timing the reference's Triton kernels on the GPU (reference_triton_gpu)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
