@@ -200,6 +200,31 @@ B200NORM_API int b200norm_softmax_bwd(const void* y, int64_t y_row_stride, const
                                       int io_dtype, void* stream);
 
 /*
+ * p-norm and normalisation over the last dimension, the reference's TritonHub.Ops.norm / normalize
+ * (Ops/norm.py, Ops/normalize.py), on (M, N) rows (the reference's (B, M, K) flattened):
+ *   b200norm_pnorm_fwd      replaces _norm_fwd (norm.py:47-60):
+ *                           norms[m] = max((sum_k |x[m,k]|^p)^(1/p), eps), stored in the storage type;
+ *   b200norm_pnorm_bwd      replaces _norm_bwd (norm.py:103-126); dout and norms are (M,) contiguous:
+ *                           p = 1: dout*sign(x); p = 2: dout*x/norms; else dout*sign(x)*|x|^(p-1)/norms^(p-1);
+ *   b200norm_normalize_fwd  replaces _normalize_fwd (normalize.py:35-59), both of its kernels in one:
+ *                           norms as above, y = x / norms with norms as stored (rounded);
+ *   b200norm_normalize_bwd  replaces _normalize_bwd (normalize.py:119-144); x is read for p = 1 and for p
+ *                           other than 2, y for every p but 1; either may be NULL where it is not read.
+ * 1 <= p <= 6 and eps >= 0 as in the reference's wrappers (norm.py:143-144); fp32 arithmetic, any
+ * alignment, rows up to 64 KB.
+ */
+B200NORM_API int b200norm_pnorm_fwd(const void* x, int64_t x_row_stride, void* norms, int64_t M, int64_t N, float p,
+                                    float eps, int io_dtype, void* stream);
+B200NORM_API int b200norm_pnorm_bwd(const void* x, int64_t x_row_stride, const void* norms, const void* dout, void* dx,
+                                    int64_t dx_row_stride, int64_t M, int64_t N, float p, int io_dtype, void* stream);
+B200NORM_API int b200norm_normalize_fwd(const void* x, int64_t x_row_stride, void* y, int64_t y_row_stride, void* norms,
+                                        int64_t M, int64_t N, float p, float eps, int io_dtype, void* stream);
+B200NORM_API int b200norm_normalize_bwd(const void* x, int64_t x_row_stride, const void* y, int64_t y_row_stride,
+                                        const void* norms, const void* dout, int64_t dout_row_stride, void* dx,
+                                        int64_t dx_row_stride, int64_t M, int64_t N, float p, int io_dtype,
+                                        void* stream);
+
+/*
  * Multi-GPU exchange fused into the backward's column reduce.  (No counterpart in the reference,
  * which is single-GPU.)  One process per GPU; every rank owns an inbox of `depth` equal slots of
  * inbox_bytes / depth each -- a slot holds one exchange's (total_shards, slots, N) fp32 at its

@@ -298,3 +298,68 @@ API void oracle_softmax_bwd(const float* y, const float* dout, float* dx, int64_
     }
   }
 }
+
+/* ---- p-norm / normalize over rows ---------------------------------------------------------- */
+
+static double sgn(double v) { return v > 0 ? 1.0 : (v < 0 ? -1.0 : 0.0); }
+
+/* _norm_fwd_kernel (TritonHub/Ops/norm.py:11-45): norms[r] = max((sum |x|^p)^(1/p), eps).  The
+ * caller rounds the result to the storage type, as the kernel's store does (norm.py:41). */
+API void oracle_pnorm_fwd(const float* x, float* norms, int64_t M, int64_t N, float p, float eps, int acc64) {
+  for (int64_t r = 0; r < M; ++r) {
+    const float* xr = x + r * N;
+    if (acc64) {
+      double acc = 0;
+      for (int64_t c = 0; c < N; ++c)
+        acc += p == 1.f ? fabs((double)xr[c]) : (p == 2.f ? (double)xr[c] * xr[c] : pow(fabs((double)xr[c]), (double)p)); /* :26-32 */
+      double n = p == 2.f ? sqrt(acc) : (p == 1.f ? acc : pow(acc, 1.0 / (double)p));                                   /* :36-39 */
+      norms[r] = (float)(n > (double)eps ? n : (double)eps);                                                             /* :40 */
+    } else {
+      float acc = 0;
+      for (int64_t c = 0; c < N; ++c) acc += p == 1.f ? fabsf(xr[c]) : (p == 2.f ? xr[c] * xr[c] : powf(fabsf(xr[c]), p));
+      float n = p == 2.f ? sqrtf(acc) : (p == 1.f ? acc : powf(acc, 1.0f / p));
+      norms[r] = n > eps ? n : eps;
+    }
+  }
+}
+
+/* _norm_bwd_kernel (norm.py:66-101); `norms` as stored by the forward. */
+API void oracle_pnorm_bwd(const float* x, const float* norms, const float* dout, float* dx, int64_t M, int64_t N,
+                          float p, int acc64) {
+  for (int64_t r = 0; r < M; ++r) {
+    const float* xr = x + r * N;
+    float* dr = dx + r * N;
+    const double g = dout[r], n = norms[r];
+    const double np1 = (p != 1.f && p != 2.f) ? pow(n, (double)p - 1.0) : n;                  /* norm.py:86-87 */
+    for (int64_t c = 0; c < N; ++c) {
+      const double v = xr[c];
+      double d;
+      if (p == 1.f) d = g * sgn(v);                                                          /* :93-95 */
+      else if (p == 2.f) d = (g * v) / n;                                                    /* :96-97 */
+      else d = (g * sgn(v) * pow(fabs(v), (double)p - 1.0)) / np1;                           /* :98-100 */
+      dr[c] = acc64 ? (float)d : (float)d;
+    }
+  }
+}
+
+/* _normalize_bwd_kernel (TritonHub/Ops/normalize.py:61-117): x the input, y the forward's output,
+ * norms as stored by the forward. */
+API void oracle_normalize_bwd(const float* x, const float* y, const float* norms, const float* dout, float* dx,
+                              int64_t M, int64_t N, float p, int acc64) {
+  (void)acc64;
+  for (int64_t r = 0; r < M; ++r) {
+    const float *xr = x + r * N, *yr = y + r * N, *gr = dout + r * N;
+    float* dr = dx + r * N;
+    const double n = norms[r];
+    double proj = 0;
+    for (int64_t c = 0; c < N; ++c) proj += (p == 1.f ? (double)xr[c] : (double)yr[c]) * gr[c];   /* :87-95 */
+    for (int64_t c = 0; c < N; ++c) {
+      const double g = gr[c];
+      double d;
+      if (p == 1.f) d = g / n - sgn(xr[c]) * (proj / (n * n));                                    /* :101-105 */
+      else if (p == 2.f) d = (g - yr[c] * proj) / n;                                              /* :106-108 */
+      else d = g / n - sgn(xr[c]) * pow(fabs((double)xr[c]), (double)p - 1.0) * (proj / (pow(n, (double)p - 1.0) * n)); /* :109-113 */
+      dr[c] = (float)d;
+    }
+  }
+}

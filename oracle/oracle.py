@@ -48,6 +48,12 @@ def _load():
         lib.oracle_softmax_fwd.argtypes = [vp, vp, i64, i64, i32, i32]
         lib.oracle_softmax_bwd.restype = None
         lib.oracle_softmax_bwd.argtypes = [vp, vp, vp, i64, i64, i32, i32]
+        lib.oracle_pnorm_fwd.restype = None
+        lib.oracle_pnorm_fwd.argtypes = [vp, vp, i64, i64, f32, f32, i32]
+        lib.oracle_pnorm_bwd.restype = None
+        lib.oracle_pnorm_bwd.argtypes = [vp, vp, vp, vp, i64, i64, f32, i32]
+        lib.oracle_normalize_bwd.restype = None
+        lib.oracle_normalize_bwd.argtypes = [vp, vp, vp, vp, vp, i64, i64, f32, i32]
         lib.oracle_set_threads.argtypes = [i32]
         lib.oracle_get_threads.restype = i32
         _lib = lib
@@ -161,6 +167,42 @@ def softmax_bwd(y, dout, *, log=False, acc64=False):
     M, N = y.shape
     dx = np.empty_like(y)
     _load().oracle_softmax_bwd(_p(y), _p(dout), _p(dx), M, N, int(log), int(acc64))
+    return dx
+
+
+def pnorm_fwd(x, *, p=2.0, eps=1e-6, dtype="fp32", acc64=False):
+    """Row p-norms of an (M, N) array, clamped to eps and rounded to the storage type as the
+    reference's store does (Ops/norm.py:11-45)."""
+    x = _as_f32(x)
+    M, N = x.shape
+    norms = np.empty(M, dtype=np.float32)
+    _load().oracle_pnorm_fwd(_p(x), _p(norms), M, N, float(p), float(eps), int(acc64))
+    return round_to(norms, dtype).astype(np.float32)
+
+
+def pnorm_bwd(x, norms, dout, *, p=2.0, acc64=True):
+    """dx of the row p-norm from x, the stored norms and dout (M,) (Ops/norm.py:66-101)."""
+    x, norms, dout = _as_f32(x), _as_f32(norms), _as_f32(dout)
+    M, N = x.shape
+    dx = np.empty_like(x)
+    _load().oracle_pnorm_bwd(_p(x), _p(norms), _p(dout), _p(dx), M, N, float(p), int(acc64))
+    return dx
+
+
+def normalize_fwd(x, *, p=2.0, eps=1e-6, dtype="fp32", acc64=False):
+    """(y, norms): norms as pnorm_fwd stores them, y = x / norms (Ops/normalize.py:11-33)."""
+    x = _as_f32(x)
+    norms = pnorm_fwd(x, p=p, eps=eps, dtype=dtype, acc64=acc64)
+    y = (x.astype(np.float64) / norms.astype(np.float64)[:, None]).astype(np.float32)
+    return y, norms
+
+
+def normalize_bwd(x, y, norms, dout, *, p=2.0, acc64=True):
+    """dx of normalize from x, the forward's output y, the stored norms and dout (Ops/normalize.py:61-117)."""
+    x, y, norms, dout = _as_f32(x), _as_f32(y), _as_f32(norms), _as_f32(dout)
+    M, N = x.shape
+    dx = np.empty_like(x)
+    _load().oracle_normalize_bwd(_p(x), _p(y), _p(norms), _p(dout), _p(dx), M, N, float(p), int(acc64))
     return dx
 
 

@@ -2,7 +2,7 @@
 
 Run once, where the reference checkout is available (it is not needed to *use* the vectors):
 
-    TRITON_INTERPRET=1 python tests/golden/make_golden.py /path/to/Triton-Hub
+    TRITON_INTERPRET=1 python tests/golden/make_golden.py /path/to/Triton-Hub [--ops-only]
 
 The reference has no stored vectors of its own and its wrappers need a GPU, so this script
 executes the reference's four Triton kernel bodies (TritonHub/Normalization/layernorm.py:14-46,
@@ -12,6 +12,7 @@ layernorm.py:63-72,176-208) with PROGRAMS standing in for the GPU's SM count.  I
 seeded; every case is written to <name>.npz together with what the reference produced.
 16-bit tensors are stored as fp16 arrays or bf16 bit patterns (uint16) to keep files small.
 """
+import importlib
 import math
 import os
 import sys
@@ -194,11 +195,65 @@ def run_chain(L, G, name, dtype, batch, N, eps, approximate):
     print(name, "ok")
 
 
+# Ops.norm / Ops.normalize (TritonHub/Ops/norm.py, normalize.py): name, dtype, B, M, K, p, eps
+OPS_CASES = [
+    ("ops_p2_fp32_2x9x128", torch.float32, 2, 9, 128, 2, 1e-12),
+    ("ops_p2_fp16_1x7x1000", torch.float16, 1, 7, 1000, 2, 1e-12),
+    ("ops_p2_bf16_1x4x4096", torch.bfloat16, 1, 4, 4096, 2, 1e-6),
+    ("ops_p1_fp32_1x6x333", torch.float32, 1, 6, 333, 1, 1e-12),
+]
+# p other than 1 and 2 goes through libdevice's pow (norm.py:4,32), which Triton's interpreter cannot
+# execute ("_semantic argument must be provided outside of JIT functions"): no golden vectors for it; the
+# oracle's general-p branch is pinned to torch.norm / F.normalize autograd in fp64 instead.
+
+
+def run_ops(NM, NZ, name, dtype, B, M, K, p, eps):
+    """The reference's host glue (norm.py:47-60, 103-126; normalize.py:35-59, 119-144) around its four
+    kernels, with one fixed block shape in place of the autotuner's choice."""
+    import triton
+    import triton.language as tl
+    tdt = {torch.float32: tl.float32, torch.float16: tl.float16, torch.bfloat16: tl.bfloat16}[dtype]
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(B, M, K, generator=g).to(dtype)
+    dn = torch.rand(B, M, generator=g).to(dtype)
+    dy = torch.randn(B, M, K, generator=g).to(dtype)
+    BM, BK = 4, 64
+    grid = (triton.cdiv(M, BM), B)
+    norms = torch.empty(B, M, dtype=dtype)
+    NM._norm_fwd_kernel.fn[grid](x, x.stride(0), x.stride(1), x.stride(2), norms, norms.stride(0), norms.stride(1),
+                                 eps, p, M, K, BLOCK_SIZE_M=BM, BLOCK_SIZE_K=BK, dtype=tdt)
+    dx_norm = torch.empty_like(x)
+    NM._norm_bwd_kernel.fn[grid](x, x.stride(0), x.stride(1), x.stride(2), norms, norms.stride(0), norms.stride(1),
+                                 dn, dn.stride(0), dn.stride(1), dx_norm, dx_norm.stride(0), dx_norm.stride(1),
+                                 p, M, K, BLOCK_SIZE_M=BM, BLOCK_SIZE_K=BK, dtype=tdt)
+    y = torch.empty_like(x)
+    NZ._normalize_fwd_kernel.fn[grid](x, x.stride(0), x.stride(1), x.stride(2), norms, norms.stride(0),
+                                      norms.stride(1), y, y.stride(0), y.stride(1), y.stride(2), M, K,
+                                      BLOCK_SIZE_M=BM, BLOCK_SIZE_K=BK, dtype=tdt)
+    dx = torch.empty_like(x)
+    NZ._normalize_bwd_kernel.fn[grid](x, x.stride(0), x.stride(1), x.stride(2), y, y.stride(0), y.stride(1),
+                                      y.stride(2), norms, norms.stride(0), norms.stride(1), dy, dy.stride(0),
+                                      dy.stride(1), dy.stride(2), dx, dx.stride(0), dx.stride(1), dx.stride(2),
+                                      p, M, K, BLOCK_SIZE_M=BM, BLOCK_SIZE_K=BK, dtype=tdt)
+    out = {}
+    for key, t in (("x", x), ("dnorm", dn), ("dy", dy), ("norms", norms), ("dx_norm", dx_norm), ("y", y), ("dx", dx)):
+        k, v = store(t)
+        out[key + k] = v
+    out["meta"] = np.array(["ops", str(dtype).replace("torch.", ""), str(p), repr(eps)])
+    np.savez_compressed(HERE / f"{name}.npz", **out)
+    print(name, "ok")
+
+
 def main():
     if len(sys.argv) < 2:
         raise SystemExit("usage: make_golden.py /path/to/Triton-Hub")
     ref = sys.argv[1]
     sys.path.insert(0, ref)
+    if "--ops-only" in sys.argv:
+        NM, NZ = importlib.import_module("TritonHub.Ops.norm"), importlib.import_module("TritonHub.Ops.normalize")
+        for case in OPS_CASES:
+            run_ops(NM, NZ, *case)
+        return
     from TritonHub.Normalization import layernorm as L
     from TritonHub.Normalization import rmsnorm as R
     from TritonHub.Activations import gelu as G
@@ -212,6 +267,10 @@ def main():
     from TritonHub.Activations import softmax as S
     for case in SOFTMAX_CASES:
         run_softmax(S, LS, *case)
+    # the package re-exports classes named like its modules, so fetch the modules themselves
+    NM, NZ = importlib.import_module("TritonHub.Ops.norm"), importlib.import_module("TritonHub.Ops.normalize")
+    for case in OPS_CASES:
+        run_ops(NM, NZ, *case)
 
 
 if __name__ == "__main__":

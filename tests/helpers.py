@@ -8,7 +8,8 @@ from oracle import oracle as O
 
 GOLDEN_DIR = Path(__file__).resolve().parent / "golden"
 _ALL_GOLDEN = sorted(p.stem for p in GOLDEN_DIR.glob("*.npz"))
-GOLDEN = [n for n in _ALL_GOLDEN if "gelu" not in n and "softmax" not in n]   # the norm kernels alone
+GOLDEN = [n for n in _ALL_GOLDEN if "gelu" not in n and "softmax" not in n and not n.startswith("ops_")]  # the norm kernels alone
+GOLDEN_OPS = [n for n in _ALL_GOLDEN if n.startswith("ops_")]                # the reference's Ops.norm / normalize kernels
 GOLDEN_SOFTMAX = [n for n in _ALL_GOLDEN if "softmax" in n]                  # the reference's softmax kernels
 GOLDEN_GELU = [n for n in _ALL_GOLDEN if n.startswith("gelu_")]          # the reference's GeLU kernels alone
 GOLDEN_CHAIN = [n for n in _ALL_GOLDEN if "_gelu_" in n and not n.startswith("gelu_")]   # LayerNorm -> GeLU

@@ -102,6 +102,15 @@ def test_dim_sweep_vs_oracle(dtype, rms):
         check_against_oracle(x, dy, w, b, 1e-5, rms=rms, dtype=dtype, label=f"N={N} ")
 
 
+@pytest.mark.parametrize("rms", [False, True])
+def test_longer_row_after_a_shorter_one_on_the_same_kernel(rms):
+    """One kernel instantiation serves a range of row lengths, each with its own staging size; a
+    shorter row in between must not shrink what a longer row may use (its launch shape is cached)."""
+    for N in (5120, 4160, 5120, 16384, 12296, 16384):
+        x, dy, w, b = make_inputs(9, N, "bf16", seed=N, has_b=not rms)
+        check_against_oracle(x, dy, w, b, 1e-5, rms=rms, dtype="bf16", label=f"N={N} ")
+
+
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
 def test_every_small_dim(dtype):
     """Every N from 1 to 257 at a few row counts: exercises each packet-count predicate and the

@@ -6,7 +6,8 @@ from .activations import GeLU, LayerNormGeLU, RMSNormGeLU, gelu, layernorm_gelu,
 from .hostio import HostPipeline
 from .modules import LayerNorm, RMSNorm
 from .softmax import LogSoftmax, Softmax, Softmin
+from .ops import norm, normalize
 
 __all__ = ['LayerNorm', 'RMSNorm', 'layernorm', 'rmsnorm', 'finalize_dwdb', 'HostPipeline', 'GeLU', 'gelu',
-           'LayerNormGeLU', 'RMSNormGeLU', 'layernorm_gelu', 'rmsnorm_gelu', 'Softmax', 'LogSoftmax', 'Softmin']
+           'LayerNormGeLU', 'RMSNormGeLU', 'layernorm_gelu', 'rmsnorm_gelu', 'Softmax', 'LogSoftmax', 'Softmin', 'norm', 'normalize']
 __version__ = '0.1.0'

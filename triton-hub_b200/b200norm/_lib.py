@@ -53,6 +53,10 @@ SIGNATURES = {
     "b200norm_gelu_bwd": (_int, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _int, _int, _vp]),
     "b200norm_softmax_fwd": (_int, [_vp, _i64, _vp, _i64, _i64, _i64, _int, _int, _vp]),
     "b200norm_softmax_bwd": (_int, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _int, _int, _vp]),
+    "b200norm_pnorm_fwd": (_int, [_vp, _i64, _vp, _i64, _i64, _f32, _f32, _int, _vp]),
+    "b200norm_pnorm_bwd": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _int, _vp]),
+    "b200norm_normalize_fwd": (_int, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _f32, _f32, _int, _vp]),
+    "b200norm_normalize_bwd": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _f32, _int, _vp]),
     "b200norm_ln_act_fwd": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _f32, _int, _int, _int, _vp]),
     "b200norm_rms_act_fwd": (_int, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _i64, _f32, _int, _int, _int, _vp]),
     "b200norm_ln_act_bwd": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _int, _vp, _sz,

@@ -1,6 +1,6 @@
 """Throughput scan of the kernels over row lengths, storage types and ops.
 
-    python -m b200norm.scan [--ops ln rms softmax logsoftmax ln_gelu] [--dtypes bf16 fp32] [--dims 1024 4096 ...]
+    python -m b200norm.scan [--ops ln rms softmax logsoftmax ln_gelu normalize pnorm] [--dtypes bf16 fp32] [--dims 1024 4096 ...]
 
 For every combination the forward and the backward are captured into a CUDA graph each (through
 the same wrappers users call) and replayed 20 times between two CUDA events; tensors hold 1 GiB
@@ -15,6 +15,7 @@ import torch
 
 from . import activations as A
 from . import functional as Fn
+from . import ops as P
 from . import softmax as S
 
 DT = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32, "fp64": torch.float64}
@@ -59,11 +60,23 @@ def scan_one(op, dtype, N, dev, gib=1.0):
         fwd = lambda: S._fwd(x, log)
         y = fwd()
         bwd = lambda: S._bwd(y, dy, log)
+    elif op == "normalize":  # p = 2: forward x -> y (2 row passes), backward y, dout -> dx (3)
+        x3, dy3 = x.reshape(1, M, N), dy.reshape(1, M, N)
+        fwd = lambda: P._normalize_fwd(x3, 2, 1e-12)
+        y3, norms = fwd()
+        bwd = lambda: P._normalize_bwd(x3, y3, norms, dy3, 2)
+    elif op == "pnorm":      # p = 2: forward reads x (1 row pass), backward x -> dx (2)
+        x3 = x.reshape(1, M, N)
+        gn = torch.rand(1, M, device=dev).to(dtype)
+        fwd = lambda: P._norm_fwd(x3, 2, 1e-12)
+        norms = fwd()
+        bwd = lambda: P._norm_bwd(x3, norms, gn, 2)
     else:
         raise ValueError(op)
     f_ms, b_ms = _time(fwd), _time(bwd)
-    f_gbs, b_gbs = M * 2 * N * es / f_ms / 1e6, M * 3 * N * es / b_ms / 1e6
-    tot = M * 5 * N * es / (f_ms + b_ms) / 1e6
+    fp, bp = (1, 2) if op == "pnorm" else (2, 3)  # row passes forward / backward
+    f_gbs, b_gbs = M * fp * N * es / f_ms / 1e6, M * bp * N * es / b_ms / 1e6
+    tot = M * (fp + bp) * N * es / (f_ms + b_ms) / 1e6
     return M, f_gbs, b_gbs, tot
 
 

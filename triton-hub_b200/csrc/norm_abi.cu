@@ -17,6 +17,7 @@
 #include "norm_fwd.cuh"
 #include "norm_push.cuh"
 #include "norm_table.h"
+#include "pnorm.cuh"
 #include "softmax.cuh"
 
 namespace b200norm {
@@ -44,6 +45,7 @@ struct DeviceState {
   int* status_dev = nullptr;
   std::mutex mu;
   std::unordered_map<unsigned long long, int> occupancy;  // (kernel, dyn smem) -> CTAs per SM
+  std::unordered_map<const void*, size_t> smem_limit;     // kernel -> dynamic shared memory it has been allowed
 };
 DeviceState g_dev[kMaxDevices];
 
@@ -80,10 +82,15 @@ int occupancy(DeviceState& s, const void* fn, int threads, size_t smem, int* out
     return B200NORM_OK;
   }
   cudaError_t e;
-  if (smem > 32 * 1024) {  // static shared memory counts toward the 48 KB default limit too
+  // Static shared memory counts toward the 48 KB default limit too, hence 32 KB.  The limit is only
+  // ever raised: one kernel serves a range of row lengths, and a shorter row after a longer one must
+  // not take the allowance away from a launch shape whose occupancy is already cached.
+  size_t& allowed = s.smem_limit[fn];
+  if (smem > 32 * 1024 && smem > allowed) {
     e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess)
       return fail(B200NORM_ERR_CUDA, "cudaFuncSetAttribute(%zu B): %s", smem, cudaGetErrorString(e));
+    allowed = smem;
   }
   int n = 0;
   if (cluster > 1) {
@@ -497,6 +504,77 @@ int softmax_impl(bool bwd, const void* x, int64_t xs, const void* dout, int64_t 
   return launch(fn, dim3(grid), dim3(256), 0, &p, s, false);
 }
 
+// p-norm and normalisation over the last dimension (TritonHub/Ops/norm.py:47-60, 103-126;
+// Ops/normalize.py:35-59, 119-144).  mode: 0 norm forward, 1 normalize forward, 2 normalize backward,
+// 3 norm backward.  `a` is the staged input of the row kernels (x, or the saved y), `x` the input where a
+// backward needs it besides.
+int pnorm_impl(int mode, const void* a, int64_t as, const void* x, int64_t xs, const void* dout, int64_t ds,
+               void* out, int64_t os, void* norms, int64_t M, int64_t N, float pw, float eps, int io_dtype,
+               void* stream) {
+  if (!valid_dtype(io_dtype)) return fail(B200NORM_ERR_ARG, "unknown dtype code %d", io_dtype);
+  if (M < 0 || N < 1) return fail(B200NORM_ERR_ARG, "bad shape M=%lld N=%lld", (long long)M, (long long)N);
+  if (!(pw >= 1.f) || !(pw <= 6.f)) return fail(B200NORM_ERR_ARG, "p must be in [1, 6] (p=%g)", (double)pw);
+  if (!(eps >= 0.f)) return fail(B200NORM_ERR_ARG, "eps must be non-negative");
+  const PnormTable* k = io_dtype == B200NORM_F32   ? pnorm_kernels_f32()
+                        : io_dtype == B200NORM_F16 ? pnorm_kernels_f16()
+                        : io_dtype == B200NORM_BF16 ? pnorm_kernels_bf16()
+                                                    : pnorm_kernels_f64();
+  const int es = k->elem_size;
+  if (N * es > kMaxRowBytes)
+    return fail(B200NORM_ERR_UNSUPPORTED, "rows wider than 64KB are not supported (N=%lld)", (long long)N);
+  if (M == 0) return B200NORM_OK;
+  const bool has_out = mode != 0, has_dout = mode >= 2;
+  const bool needs_x = mode == 3 || (mode == 2 && pw != 1.f && pw != 2.f);
+  if (!norms || (mode != 3 && !a) || (has_out && !out) || (has_dout && !dout) || (needs_x && !x))
+    return fail(B200NORM_ERR_ARG, "null input / output");
+  if ((mode != 3 && as < N) || (has_out && os < N) || (mode == 2 && ds < N) || (needs_x && xs < N))
+    return fail(B200NORM_ERR_ARG, "row stride smaller than N");
+  DeviceState* dev;
+  if (int rc = device_state(&dev)) return rc;
+  PnormParams p;
+  p.a = a; p.dout = dout; p.x = x; p.out = out; p.norms = norms;
+  p.a_stride = as; p.dout_stride = ds; p.x_stride = xs; p.out_stride = os;
+  p.M = M; p.N = static_cast<int>(N); p.V = static_cast<int>(N * es / 16); p.p = pw; p.eps = eps;
+  p.lanes_log2 = 0; p.status = dev->status_dev;
+  const bool p2 = pw == 2.f;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool packets = (N * es) % 16 == 0 && (mode == 3 || aligned16(a, as, es)) && (!has_out || aligned16(out, os, es)) &&
+                       (mode != 2 || aligned16(dout, ds, es)) && (!needs_x || aligned16(x, xs, es));
+  if (packets && mode == 3) {
+    while ((1 << p.lanes_log2) < p.V && p.lanes_log2 < 8) ++p.lanes_log2;
+    const void* fn = k->norm_bwd[p2 ? 1 : 0];
+    const int rows_per_cta = 256 >> p.lanes_log2;
+    int occ;
+    if (int rc = occupancy(*dev, fn, 256, 0, &occ)) return rc;
+    const int64_t want = (M + rows_per_cta - 1) / rows_per_cta;
+    const int grid = static_cast<int>(std::min<int64_t>(want, (int64_t)dev->sm_count * occ));
+    return launch(fn, dim3(grid), dim3(256), 0, &p, s);
+  }
+  if (packets) {
+    const PnormKernel* pk = nullptr;
+    // Tuning aid: B200NORM_FORCE_PNORM = index of the table entry to use when it can hold the row.
+    static const int forced = std::getenv("B200NORM_FORCE_PNORM") ? std::atoi(std::getenv("B200NORM_FORCE_PNORM")) : -1;
+    if (forced >= 0 && forced < k->n && k->kernels[forced].capacity() >= p.V) pk = &k->kernels[forced];
+    for (int i = 0; i < k->n && pk == nullptr; ++i)
+      if (k->kernels[i].capacity() >= p.V) pk = &k->kernels[i];
+    if (pk != nullptr) {
+      const void* fn = pk->fn[mode][p2 ? 1 : 0];
+      const int stages = mode == 2 ? pk->stages_bwd : pk->stages_fwd;
+      const size_t smem = static_cast<size_t>(pk->warps_m) * stages * (mode == 2 ? 2 : 1) * p.V * 16;
+      int occ;
+      if (int rc = occupancy(*dev, fn, pk->threads(), smem, &occ)) return rc;
+      const int64_t want = (M + pk->rows_per_cta() - 1) / pk->rows_per_cta();
+      const int grid = static_cast<int>(std::min<int64_t>(want, (int64_t)dev->sm_count * occ));
+      return launch(fn, dim3(grid), dim3(pk->threads()), smem, &p, s);
+    }
+  }
+  const void* fn = k->any[mode];
+  int occ;
+  if (int rc = occupancy(*dev, fn, 256, 0, &occ)) return rc;
+  const int grid = static_cast<int>(std::min<int64_t>(M, (int64_t)dev->sm_count * occ));
+  return launch(fn, dim3(grid), dim3(256), 0, &p, s, false);
+}
+
 // ---------------------------------------------------------------------------------------
 // RMSNorm backward with built-in scratch (b200norm_rms_bwd_static): for hosts that plan their
 // device memory once and cannot hand over, or allocate, a workspace per call.
@@ -770,6 +848,31 @@ int b200norm_gelu_bwd(const void* x, int64_t x_row_stride, const void* dout, int
                       int64_t dx_row_stride, int64_t M, int64_t N, int approximate, int io_dtype, void* stream) {
   return act_impl(true, x, x_row_stride, dout, dout_row_stride, dx, dx_row_stride, M, N, approximate, io_dtype,
                   stream);
+}
+
+int b200norm_pnorm_fwd(const void* x, int64_t x_row_stride, void* norms, int64_t M, int64_t N, float p, float eps,
+                       int io_dtype, void* stream) {
+  return pnorm_impl(0, x, x_row_stride, nullptr, 0, nullptr, 0, nullptr, 0, norms, M, N, p, eps, io_dtype, stream);
+}
+
+int b200norm_pnorm_bwd(const void* x, int64_t x_row_stride, const void* norms, const void* dout, void* dx,
+                       int64_t dx_row_stride, int64_t M, int64_t N, float p, int io_dtype, void* stream) {
+  return pnorm_impl(3, nullptr, 0, x, x_row_stride, dout, 0, dx, dx_row_stride, const_cast<void*>(norms), M, N, p, 0.f,
+                    io_dtype, stream);
+}
+
+int b200norm_normalize_fwd(const void* x, int64_t x_row_stride, void* y, int64_t y_row_stride, void* norms, int64_t M,
+                           int64_t N, float p, float eps, int io_dtype, void* stream) {
+  return pnorm_impl(1, x, x_row_stride, nullptr, 0, nullptr, 0, y, y_row_stride, norms, M, N, p, eps, io_dtype, stream);
+}
+
+int b200norm_normalize_bwd(const void* x, int64_t x_row_stride, const void* y, int64_t y_row_stride, const void* norms,
+                           const void* dout, int64_t dout_row_stride, void* dx, int64_t dx_row_stride, int64_t M,
+                           int64_t N, float p, int io_dtype, void* stream) {
+  // the projection sum runs over x for p = 1 and over the saved output otherwise (normalize.py:87-95)
+  const bool p1 = p == 1.f;
+  return pnorm_impl(2, p1 ? x : y, p1 ? x_row_stride : y_row_stride, x, x_row_stride, dout, dout_row_stride, dx,
+                    dx_row_stride, const_cast<void*>(norms), M, N, p, 0.f, io_dtype, stream);
 }
 
 int b200norm_softmax_fwd(const void* x, int64_t x_row_stride, void* y, int64_t y_row_stride, int64_t M, int64_t N,

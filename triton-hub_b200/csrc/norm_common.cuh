@@ -108,6 +108,10 @@ __device__ __forceinline__ float rcp_fast(float x) {
   return y;
 }
 
+// Makes the compiler forget what it knows about a packet, so that a later unpack is redone from
+// the packed registers instead of keeping every fp32 copy alive across the row reduction.
+__device__ __forceinline__ void forget(uint4& v) { asm volatile("" : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)); }
+
 // Scalar conversions for the any-alignment kernels.
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }

@@ -54,6 +54,29 @@ const SoftmaxTable* softmax_kernels_f16();
 const SoftmaxTable* softmax_kernels_bf16();
 const SoftmaxTable* softmax_kernels_f64();
 
+// p-norm / normalize over the last dimension: fn[mode][p == 2], mode 0 norm forward, 1 normalize
+// forward, 2 normalize backward; the element-wise norm backward and the any-alignment kernels apart.
+struct PnormKernel {
+  int ldgs, warps_m, warps_n;
+  int stages_fwd, stages_bwd;
+  int lanes;
+  const void* fn[3][2];
+  int capacity() const { return ldgs * lanes * warps_n; }
+  int threads() const { return 32 * warps_m * warps_n; }
+  int rows_per_cta() const { return warps_m * (32 / lanes); }
+};
+struct PnormTable {
+  int elem_size;
+  const PnormKernel* kernels;  // ascending capacity
+  int n;
+  const void* norm_bwd[2];  // [p == 2]
+  const void* any[4];       // modes 0-2 as above, 3 norm backward
+};
+const PnormTable* pnorm_kernels_f32();
+const PnormTable* pnorm_kernels_f16();
+const PnormTable* pnorm_kernels_bf16();
+const PnormTable* pnorm_kernels_f64();
+
 // One table per (storage type, fused activation: 0 none, 1 GeLU erf, 2 GeLU tanh).
 #define B200NORM_DECLARE_TABLES(name)      \
   const DTypeKernels* kernels_##name##_act0(); \

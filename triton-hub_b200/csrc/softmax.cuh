@@ -135,10 +135,6 @@ struct PackedMax<__nv_bfloat16> {
   }
 };
 
-// Makes the compiler forget what it knows about a packet, so that a later unpack is redone from
-// the packed registers instead of keeping every fp32 copy alive across the row reduction.
-__device__ __forceinline__ void forget(uint4& v) { asm volatile("" : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)); }
-
 template <int LANES>
 __device__ __forceinline__ float lanes_add(float v) {
 #pragma unroll
