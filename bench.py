@@ -51,7 +51,7 @@ ESIZE = {"fp32": 4, "fp16": 2, "bf16": 2, "fp64": 8}
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per row (dram__bytes_read.sum + dram__bytes_write.sum) of the backward kernel, from the
 # ncu captures summarised under profiles/ (taken at 16384, 16384 and 4096 rows; traffic is proportional to rows).
-NCU_BWD_DRAM_BYTES_PER_ROW = {"c2": 22415.0, "c3": 28811.0, "c4": 91065.0}
+NCU_BWD_DRAM_BYTES_PER_ROW = {"c2": 22365.0, "c3": 28811.0, "c4": 91065.0}
 
 
 def algorithmic_bytes(wl, rows):
