@@ -52,8 +52,10 @@ struct ColReducePushParams {
   int N;
 };
 
-__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
-  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+// A flag store with no ordering of its own: the caller has already fenced at system scope.  (A
+// st.release per peer would repeat that fence world times, one NVLink round trip each.)
+__device__ __forceinline__ void st_relaxed_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
   unsigned long long v;
@@ -103,9 +105,11 @@ __global__ void __launch_bounds__(512) colreduce_push_kernel(const ColReducePush
     if (prev == total - 1) {
       p.peers.local->push_ctas[buf] = 0;  // ready for this slot's next use
       p.peers.local->push_seq = seq;      // every CTA of this launch has read the old value by now
+      // One fence for all flags: it takes in the other CTAs' fenced stores (seen through the counter)
+      // and this CTA's own, and orders them before the flag stores below.
       __threadfence_system();
       for (int r = 0; r < p.peers.world; ++r)
-        st_release_sys(&p.peers.flags[r][(size_t)buf * p.peers.world + p.peers.rank], seq);
+        st_relaxed_sys(&p.peers.flags[r][(size_t)buf * p.peers.world + p.peers.rank], seq);
     }
   }
 }
@@ -157,7 +161,7 @@ __global__ void __launch_bounds__(512) colreduce4_push_kernel(const ColReducePus
       p.peers.local->push_seq = seq;
       __threadfence_system();
       for (int r = 0; r < p.peers.world; ++r)
-        st_release_sys(&p.peers.flags[r][(size_t)buf * p.peers.world + p.peers.rank], seq);
+        st_relaxed_sys(&p.peers.flags[r][(size_t)buf * p.peers.world + p.peers.rank], seq);
     }
   }
 }
