@@ -14,6 +14,12 @@
  *   the launch table behind them replaces get_cuda_autotune_config(block_keys=None)
  *                                                TritonHub/autotune.py:61-65
  *
+ * and, for the steps either side of the norm, where these stand (each documented at its declaration):
+ *
+ *   b200norm_gelu_fwd/_bwd, b200norm_{ln,rms}_act_fwd/_bwd     TritonHub/Activations/gelu.py
+ *   b200norm_softmax_fwd/_bwd                                  TritonHub/Activations/softmax.py, logsoftmax.py, softmin.py
+ *   b200norm_pnorm_fwd/_bwd, b200norm_normalize_fwd/_bwd       TritonHub/Ops/norm.py, normalize.py
+ *
  * Conventions shared by every entry point
  *   - Rows are the flattened leading dimensions: x is (M, N) with unit column stride and a
  *     row stride given in ELEMENTS (>= N).  y, dy and dx likewise.
