@@ -10,33 +10,44 @@ namespace b200norm {
 
 enum : int { kActNone = 0, kActGeluErf = 1, kActGeluTanh = 2 };
 
-// tanh(u) as 1 - 2 / (exp(2u) + 1): the reference's (e - 1) / (e + 1) (gelu.py:24) is inf / inf
-// = NaN once exp(2u) overflows (x > ~10 in fp32); this form saturates to 1 instead and agrees
-// with it wherever the reference is finite.
-__device__ __forceinline__ float tanh_via_exp(float u) {
-  const float e = ex2_fast(u * (2.f * kLog2e));
-  return fmaf(-2.f, rcp_fast(e + 1.f), 1.f);  // e = inf gives 1
+// Both forms are evaluated through one quantity each, chosen so that an element costs as few
+// instructions as the formulas allow (these kernels are issue-bound, not HBM-bound, once an
+// activation is fused in):
+//
+// tanh form (gelu.py:20-25, 67-73).  With u = k (x + 0.044715 x^3) and r = 1 / (exp(2u) + 1):
+//   tanh(u) = 1 - 2r,  gelu = 0.5 x (1 + tanh u) = x - x r,
+//   gelu'   = 0.5 (1 + tanh u + x (1 - tanh^2 u) u') = s + x u' * 2 r s,   s = 1 - r.
+// The reference's tanh, (e - 1) / (e + 1) (gelu.py:24), is inf / inf = NaN once exp(2u) overflows
+// (x > ~10 in fp32); r simply becomes 0 there, and the two agree wherever the reference is finite.
+//
+// erf form (gelu.py:27, 75-78).  Abramowitz & Stegun 7.1.26 gives erfc(|s|) = poly(t) exp(-s^2),
+// t = 1 / (1 + 0.3275911 |s|), absolute error <= 1.5e-7, one reciprocal and five FMAs -- a third of
+// the instructions of the library erff.  With q = 0.5 erfc(|x| / sqrt 2):
+//   Phi(x) = x >= 0 ? 1 - q : q,   gelu = x Phi(x) = max(x, 0) - |x| q,   gelu' = Phi(x) + x phi(x).
+constexpr float kGeluK = 0.79788456080286536f;  // sqrt(2 / pi)
+
+// r = 1 / (exp(2u) + 1) for the tanh form; x2 = x * x
+__device__ __forceinline__ float gelu_tanh_r(float x, float x2) {
+  const float arg = x * fmaf(x2, kGeluK * 0.044715f * 2.f * kLog2e, kGeluK * 2.f * kLog2e);  // 2u * log2(e)
+  return rcp_fast(ex2_fast(arg) + 1.f);  // exp = inf gives 0, exp = 0 gives 1
 }
 
-// erf(s) for s = x / sqrt(2), from e = exp(-s*s) which the caller also needs for the Gaussian density.
-// Abramowitz & Stegun 7.1.26 (five-term rational-exponential fit): absolute error <= 1.5e-7 over the
-// whole line, one reciprocal, five FMAs -- a third of the instructions of the library erff, which
-// matters because these kernels are otherwise limited by HBM, not by arithmetic.
-__device__ __forceinline__ float erf_from_exp(float s, float e) {
-  const float t = rcp_fast(fmaf(0.3275911f, fabsf(s), 1.f));
-  const float poly =
-      t * (0.254829592f + t * (-0.284496736f + t * (1.421413741f + t * (-1.453152027f + t * 1.061405429f))));
-  return copysignf(1.f - poly * e, s);
+// q = 0.5 * erfc(|x| / sqrt(2)) and e = exp(-x^2 / 2) for the erf form
+__device__ __forceinline__ float gelu_erf_q(float x, float& e) {
+  e = ex2_fast(x * x * (-0.5f * kLog2e));
+  const float t = rcp_fast(fmaf(0.3275911f * 0.70710678118654752f, fabsf(x), 1.f));
+  const float half_poly = t * (0.127414796f + t * (-0.142248368f + t * (0.7107068705f + t * (-0.7265760135f + t * 0.5307027145f))));
+  return half_poly * e;
 }
 
 template <int ACT>
 __device__ __forceinline__ float act_fwd(float x) {
   if (ACT == kActGeluErf) {
-    const float s = x * 0.70710678118654752f;
-    return 0.5f * x * (1.f + erf_from_exp(s, ex2_fast(x * x * (-0.5f * kLog2e))));  // gelu.py:27
+    float e;
+    const float q = gelu_erf_q(x, e);
+    return fmaf(-fabsf(x), q, fmaxf(x, 0.f));
   } else if (ACT == kActGeluTanh) {
-    const float inner = 0.79788456080286536f * (x + 0.044715f * x * x * x);  // gelu.py:22
-    return 0.5f * x * (1.f + tanh_via_exp(inner));                           // gelu.py:25
+    return fmaf(-x, gelu_tanh_r(x, x * x), x);
   }
   return x;
 }
@@ -45,16 +56,16 @@ __device__ __forceinline__ float act_fwd(float x) {
 template <int ACT>
 __device__ __forceinline__ float act_grad(float x) {
   if (ACT == kActGeluErf) {
-    const float s = x * 0.70710678118654752f;
-    const float e = ex2_fast(x * x * (-0.5f * kLog2e));                    // exp(-x^2 / 2), used twice
-    const float cdf = 0.5f * (1.f + erf_from_exp(s, e));                   // gelu.py:76
-    const float pdf = e * 0.39894228040143268f;                            // gelu.py:77
-    return cdf + x * pdf;                                                  // gelu.py:78
+    float e;
+    const float q = gelu_erf_q(x, e);
+    const float cdf = x >= 0.f ? 1.f - q : q;
+    return fmaf(x, e * 0.39894228040143268f, cdf);  // Phi + x * phi
   } else if (ACT == kActGeluTanh) {
-    const float k = 0.79788456080286536f;
-    const float th = tanh_via_exp(k * (x + 0.044715f * x * x * x));       // gelu.py:69-71
-    const float gp = k * (1.f + 3.f * 0.044715f * x * x);                  // gelu.py:72
-    return 0.5f * (1.f + th + x * (1.f - th * th) * gp);                   // gelu.py:73
+    const float x2 = x * x;
+    const float r = gelu_tanh_r(x, x2);
+    const float s = 1.f - r;
+    const float xup2 = x * fmaf(x2, 2.f * 3.f * 0.044715f * kGeluK, 2.f * kGeluK);  // 2 x u'
+    return fmaf(xup2, r * s, s);
   }
   return 1.f;
 }
