@@ -7,7 +7,8 @@ repository's drop-in package of the same name never share an interpreter:
     python baseline/time_reference_gpu.py ln|rms dtype M N eps mu sigma reps
 
 The first calls trigger the reference's autotuning (five launch shapes per kernel); they are
-warm-up.  Timing: CUDA events around `reps` forward+backward steps on device-resident tensors.
+warm-up.  Timing: CUDA events around `reps` forward+backward steps on device-resident tensors, the
+best of three such loops.
 """
 import json
 import sys
@@ -57,14 +58,17 @@ def main():
     for _ in range(3):
         one()
     torch.cuda.synchronize()
-    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s.record()
-    for _ in range(reps):
-        one()
-    e.record()
-    torch.cuda.synchronize()
+    best = float("inf")
+    for _ in range(3):  # the best of three timed loops: the reference gets the benefit of the doubt
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(reps):
+            one()
+        e.record()
+        torch.cuda.synchronize()
+        best = min(best, s.elapsed_time(e) / reps)
     import triton
-    print(json.dumps({"ms_per_step": s.elapsed_time(e) / reps, "steps": reps, "triton": triton.__version__,
+    print(json.dumps({"ms_per_step": best, "steps": reps, "trials": 3, "triton": triton.__version__,
                       "torch": torch.__version__}))
 
 
