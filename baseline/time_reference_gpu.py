@@ -22,6 +22,9 @@ def main():
     M, N = int(sys.argv[3]), int(sys.argv[4])
     eps, mu, sigma = float(sys.argv[5]), float(sys.argv[6]), float(sys.argv[7])
     reps = int(sys.argv[8])
+    if M * N >= 2 ** 31:  # the reference's `row * stride` is 32-bit: out-of-bounds accesses from here on
+        print(json.dumps({"unavailable": "the reference overflows its 32-bit row offsets at this size"}))
+        return
     if not (REF / "TritonHub").is_dir():
         print(json.dumps({"unavailable": "baseline/_ref holds no installed reference"}))
         return

@@ -522,10 +522,16 @@ def reference_triton_gpu(wl, rows, step_bytes, reps=10, timeout_s=420):
     """The reference's own Triton kernels on this GPU (its modules, unmodified, from baseline/_ref),
     timed in a child process by baseline/time_reference_gpu.py: the kernels this library replaces."""
     import subprocess
+    kind = "TritonHub 1.1.1 " + ("LayerNorm" if wl["op"] == "ln" else "RMSNorm") + " module (Triton JIT, autotuned), CUDA, eager"
+    if rows * wl["N"] >= 2 ** 31:
+        # `row * stride_X_row` in the reference's kernels (rmsnorm.py:26-27, layernorm.py:27-28) is 32-bit:
+        # from 2^31 elements on it wraps and the kernel reads and writes out of bounds.
+        return {"kind": kind, "unavailable": "not run: the reference's kernels index rows with a 32-bit "
+                f"row * stride, which overflows at {rows} x {wl['N']} elements (it faulted with an illegal memory "
+                "access when run at this size)"}
     script = ROOT / "baseline" / "time_reference_gpu.py"
     cmd = [sys.executable, str(script), wl["op"], wl["dtype"], str(rows), str(wl["N"]), str(wl["eps"]),
            str(wl["mu"]), str(wl["sigma"]), str(reps)]
-    kind = "TritonHub 1.1.1 " + ("LayerNorm" if wl["op"] == "ln" else "RMSNorm") + " module (Triton JIT, autotuned), CUDA, eager"
     try:
         res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout_s)
         last = [ln for ln in res.stdout.splitlines() if ln.startswith("{")]
