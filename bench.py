@@ -527,8 +527,8 @@ def reference_triton_gpu(wl, rows, step_bytes, reps=10, timeout_s=420):
         # `row * stride_X_row` in the reference's kernels (rmsnorm.py:26-27, layernorm.py:27-28) is 32-bit:
         # from 2^31 elements on it wraps and the kernel reads and writes out of bounds.
         return {"kind": kind, "unavailable": "not run: the reference's kernels index rows with a 32-bit "
-                f"row * stride, which overflows at {rows} x {wl['N']} elements (it faulted with an illegal memory "
-                "access when run at this size)"}
+                f"row * stride, which overflows at {rows} x {wl['N']} elements (its one run at such a size ended "
+                "with a CUDA error)"}
     script = ROOT / "baseline" / "time_reference_gpu.py"
     cmd = [sys.executable, str(script), wl["op"], wl["dtype"], str(rows), str(wl["N"]), str(wl["eps"]),
            str(wl["mu"]), str(wl["sigma"]), str(reps)]
@@ -536,8 +536,9 @@ def reference_triton_gpu(wl, rows, step_bytes, reps=10, timeout_s=420):
         res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout_s)
         last = [ln for ln in res.stdout.splitlines() if ln.startswith("{")]
         if res.returncode != 0 or not last:
-            tail = (res.stderr.strip().splitlines() or ["no output"])[-1]
-            return {"kind": kind, "unavailable": f"exit {res.returncode}: {tail[:160]}"}
+            lines = res.stderr.strip().splitlines() or ["no output"]
+            named = [ln for ln in lines if "error" in ln.lower()]  # the line that names the error, if any
+            return {"kind": kind, "unavailable": f"exit {res.returncode}: {(named[0] if named else lines[-1])[:200]}"}
         out = json.loads(last[-1])
         if "unavailable" in out:
             return {"kind": kind, **out}
