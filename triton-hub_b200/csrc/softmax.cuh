@@ -18,10 +18,6 @@
 
 // 16-bit Softmax forward: 1 keeps the exponentials of pass 1 in registers and scales them, 0
 // recomputes them from the packed row (fewer registers, one more exponential per element).
-// 1: the direct-load forward requests the next row before working on the current one.
-#ifndef B200NORM_SOFTMAX_PREFETCH
-#define B200NORM_SOFTMAX_PREFETCH 0
-#endif
 #ifndef B200NORM_SOFTMAX_HOLD16
 #define B200NORM_SOFTMAX_HOLD16 1
 #endif
@@ -203,21 +199,6 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) softmax_kernel(co
   int slot = 0;
   uint32_t parity = 0;
 
-  // Direct-load forward on full-warp rows: the next row's packets are requested before this row is
-  // worked on (twice the bytes in flight per thread for LDGS more registers).
-  constexpr bool PF = B200NORM_SOFTMAX_PREFETCH && STAGES == 0 && !BWD && LANES == 32;
-  uint4 nx[PF ? LDGS : 1];
-  auto request = [&](int64_t at, uint4* dst) {
-    const uint4* xrow = reinterpret_cast<const uint4*>(xb + at * p.x_stride);
-#pragma unroll
-    for (int j = 0; j < LDGS; ++j) {
-      const int v = j * TPR + t;
-      dst[j] = make_uint4(0, 0, 0, 0);
-      if (v < p.V) dst[j] = ld_stream(xrow + v);
-    }
-  };
-  if (PF && first < p.M) request(first, nx);
-
   for (int64_t base = first; base < p.M; base += step) {
     const int64_t row = base + sub;
     const bool valid = row < p.M;
@@ -225,11 +206,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) softmax_kernel(co
     // The row stays PACKED in registers and is unpacked where it is used: LogSoftmax needs x again
     // after the reduction, and holding it as fp32 next to the exponentials would halve occupancy.
     uint4 px[LDGS], pg[BWD ? LDGS : 1];
-    if (PF) {
-#pragma unroll
-      for (int j = 0; j < LDGS; ++j) px[j] = nx[j];
-      if (base + step < p.M) request(base + step, nx);
-    } else if (STAGES > 0) {
+    if (STAGES > 0) {
       mbar_wait(&bars[slot], parity, &cta_abort, p.status);
       const uint4* sx = reinterpret_cast<const uint4*>(slots + (size_t)slot * ROWS * row_bytes);
       const uint4* sg = reinterpret_cast<const uint4*>(slots + (size_t)slot * ROWS * row_bytes + row_bytes);
