@@ -224,7 +224,7 @@ int fwd_impl(int op, const void* x, int64_t xs, const void* w, const void* b, vo
   if (M == 0) return B200NORM_OK;
   if (!x || !y || !rstd || (op == kLN && !mean)) return fail(B200NORM_ERR_ARG, "null x / y / mean / rstd");
   if (xs < N || ys < N) return fail(B200NORM_ERR_ARG, "row stride smaller than N");
-  DeviceState* dev;
+  DeviceState* dev = nullptr;
   if (int rc = device_state(&dev)) return rc;
   const DTypeKernels* k = kernels_for(io_dtype, act);
   const int es = k->elem_size;
@@ -298,7 +298,7 @@ size_t partial_bytes(int64_t P, int64_t N) {
   return (static_cast<size_t>(P) * N * sizeof(float) + 255) & ~static_cast<size_t>(255);
 }
 
-int check_peers(const b200norm_peers* peers, uint64_t seq, int slots, int64_t N, int row_shards) {
+int check_peers(const b200norm_peers* peers, int slots, int64_t N, int row_shards) {
   if (peers->world < 1 || peers->world > B200NORM_MAX_PEERS || peers->rank < 0 || peers->rank >= peers->world)
     return fail(B200NORM_ERR_ARG, "peers: bad world / rank (%d / %d)", peers->world, peers->rank);
   if (peers->depth < 3 || peers->depth > 8)
@@ -337,7 +337,7 @@ int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, con
   if (int rc = check_common(M, N, io_dtype, w_dtype)) return rc;
   if (!valid_act(act)) return fail(B200NORM_ERR_ARG, "unknown activation code %d", act);
   if (peers != nullptr) {
-    if (int rc = check_peers(peers, seq, (op == kLN) ? 2 : 1, N, row_shards)) return rc;
+    if (int rc = check_peers(peers, (op == kLN) ? 2 : 1, N, row_shards)) return rc;
   }
   if (row_shards < 1 || M % row_shards != 0)
     return fail(B200NORM_ERR_ARG, "row_shards=%d must be >= 1 and divide M=%lld", row_shards, (long long)M);
@@ -347,7 +347,7 @@ int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, con
   if (op == kRMS) db = nullptr;
   const bool want_params = dw != nullptr || db != nullptr || group_sums != nullptr || peers != nullptr;
   if (M == 0 && !want_params) return B200NORM_OK;
-  DeviceState* dev;
+  DeviceState* dev = nullptr;
   if (int rc = device_state(&dev)) return rc;
   const DTypeKernels* k = kernels_for(io_dtype, act);
   const int es = k->elem_size;
@@ -436,7 +436,7 @@ int act_impl(bool bwd, const void* x, int64_t xs, const void* dout, int64_t ds, 
   if (M == 0) return B200NORM_OK;
   if (!x || !out || (bwd && !dout)) return fail(B200NORM_ERR_ARG, "null x / dout / output");
   if (xs < N || os < N || (bwd && ds < N)) return fail(B200NORM_ERR_ARG, "row stride smaller than N");
-  DeviceState* dev;
+  DeviceState* dev = nullptr;
   if (int rc = device_state(&dev)) return rc;
   const DTypeKernels* k = kernels_for(io_dtype, approximate == 0 ? B200NORM_ACT_GELU_ERF : B200NORM_ACT_GELU_TANH);
   const int es = k->elem_size;
@@ -471,7 +471,7 @@ int softmax_impl(bool bwd, const void* x, int64_t xs, const void* dout, int64_t 
   if (M == 0) return B200NORM_OK;
   if (!x || !out || (bwd && !dout)) return fail(B200NORM_ERR_ARG, "null x / dout / output");
   if (xs < N || os < N || (bwd && ds < N)) return fail(B200NORM_ERR_ARG, "row stride smaller than N");
-  DeviceState* dev;
+  DeviceState* dev = nullptr;
   if (int rc = device_state(&dev)) return rc;
   SoftmaxParams p;
   p.x = x; p.dout = dout; p.out = out;
@@ -529,7 +529,7 @@ int pnorm_impl(int mode, const void* a, int64_t as, const void* x, int64_t xs, c
     return fail(B200NORM_ERR_ARG, "null input / output");
   if ((mode != 3 && as < N) || (has_out && os < N) || (mode == 2 && ds < N) || (needs_x && xs < N))
     return fail(B200NORM_ERR_ARG, "row stride smaller than N");
-  DeviceState* dev;
+  DeviceState* dev = nullptr;
   if (int rc = device_state(&dev)) return rc;
   PnormParams p;
   p.a = a; p.dout = dout; p.x = x; p.out = out; p.norms = norms;
@@ -691,7 +691,7 @@ int b200norm_version(void) { return B200NORM_VERSION; }
 const char* b200norm_last_error(void) { return g_err; }
 
 int b200norm_query(int* sm_count, int* max_partials) {
-  DeviceState* dev;
+  DeviceState* dev = nullptr;
   if (int rc = device_state(&dev)) return rc;
   if (sm_count) *sm_count = dev->sm_count;
   if (max_partials) *max_partials = std::max(256, dev->sm_count * 16);
@@ -699,7 +699,7 @@ int b200norm_query(int* sm_count, int* max_partials) {
 }
 
 int b200norm_device_status(int clear) {
-  DeviceState* dev;
+  DeviceState* dev = nullptr;
   if (device_state(&dev)) return -1;
   const int v = *static_cast<volatile int*>(dev->status_host);
   if (clear) *static_cast<volatile int*>(dev->status_host) = 0;
@@ -708,7 +708,7 @@ int b200norm_device_status(int clear) {
 
 size_t b200norm_bwd_workspace_bytes(int64_t M, int64_t N, int io_dtype, int row_shards) {
   if (check_common(M, N, io_dtype, B200NORM_F32) || row_shards < 1 || M % row_shards != 0) return 0;
-  DeviceState* dev;
+  DeviceState* dev = nullptr;
   if (device_state(&dev)) return 0;
   const DTypeKernels* k = kernels_for(io_dtype);
   const int64_t rps = M / row_shards;
@@ -789,8 +789,8 @@ int b200norm_finalize_pushed(const b200norm_peers* peers, uint64_t seq, int slot
                              int w_dtype, void* stream) {
   if (peers == nullptr || (slots != 1 && slots != 2) || N < 1 || !valid_dtype(w_dtype))
     return fail(B200NORM_ERR_ARG, "bad finalize_pushed arguments (slots=%d N=%lld)", slots, (long long)N);
-  if (int rc = check_peers(peers, seq, slots, N, 0)) return rc;
-  DeviceState* dev;
+  if (int rc = check_peers(peers, slots, N, 0)) return rc;
+  DeviceState* dev = nullptr;
   if (int rc = device_state(&dev)) return rc;
   FinalizePushedParams p;
   p.inbox = static_cast<const float*>(peers->inbox[peers->rank]);
