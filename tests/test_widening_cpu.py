@@ -70,3 +70,13 @@ def test_abi_argument_checks_of_the_widened_entry_points():
     assert lib.b200norm_pnorm_fwd(None, 8, None, 0, 8, 2.0, 1e-6, _lib.F32, None) == _lib.OK
     assert lib.b200norm_normalize_bwd(None, 8, None, 8, None, None, 8, None, 8, 0, 8, 2.0, _lib.F32, None) == _lib.OK
     assert lib.b200norm_softmax_bwd(None, 8, None, 8, None, 8, 0, 8, 1, _lib.F32, None) == _lib.OK
+
+
+def test_a_missing_library_fails_loudly(monkeypatch, tmp_path):
+    """No fallback of any kind: without libb200norm.so the first use raises and says how to build it."""
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "libb200norm.so")
+    with pytest.raises(RuntimeError, match="is missing: build it with"):
+        _lib.load()
+    with pytest.raises(RuntimeError, match="is missing"):
+        _lib.check(_lib.ERR_ARG)
