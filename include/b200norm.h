@@ -46,7 +46,7 @@
 extern "C" {
 #endif
 
-#define B200NORM_VERSION 100 /* major*10000 + minor*100 + patch */
+#define B200NORM_VERSION 101 /* major*10000 + minor*100 + patch */
 
 #if defined(__GNUC__)
 #define B200NORM_API __attribute__((visibility("default")))
@@ -233,45 +233,72 @@ B200NORM_API int b200norm_normalize_bwd(const void* x, int64_t x_row_stride, con
 /*
  * Multi-GPU exchange fused into the backward's column reduce.  (No counterpart in the reference,
  * which is single-GPU.)  One process per GPU; every rank owns an inbox of `depth` equal slots of
- * inbox_bytes / depth each -- a slot holds one exchange's (total_shards, slots, N) fp32 at its
- * start -- and a flag array (depth, world) u64, in memory that is
- * peer-mapped into all ranks (CUDA IPC / VMM -- torch.distributed._symmetric_memory provides it).
+ * inbox_bytes / depth each, in memory that is peer-mapped into all ranks (CUDA IPC / VMM --
+ * torch.distributed._symmetric_memory provides it).  A slot holds one exchange's
+ * (total_shards, slots, N) shard sums as 8-byte entries {fp32 value, 32-bit tag of the exchange
+ * number}; an entry is written with one store, so a matching tag vouches for its value and the
+ * exchange needs neither flags nor fences.
  *
  * b200norm_*_bwd_push: like b200norm_*_bwd, but instead of writing dw / db the column-reduce
  *   kernel stores this rank's fp32 shard sums directly into slot `seq % depth` of EVERY rank's
- *   inbox (plain stores over NVLink, no loads from remote memory) and then raises this rank's
- *   flag on every rank to `seq`.  This rank fills shards [rank*row_shards, (rank+1)*row_shards);
- *   world * row_shards must equal peers->total_shards.
- * b200norm_finalize_pushed: waits (bounded, 2 s) until all `world` flags of slot `seq % depth`
- *   have reached `seq`, then adds the total_shards sums left to right in fp32 and casts to
- *   w_dtype.  Same bits on every rank and as a single GPU summing the same shards.
+ *   inbox (plain stores over NVLink, no loads from remote memory).  This rank fills shards
+ *   [rank*row_shards, (rank+1)*row_shards); world * row_shards must equal peers->total_shards.
+ *   With `finish` non-NULL the same kernel then finishes an exchange (see below) -- an earlier one
+ *   (the usual pipeline: exchange s finishes s - 1, whose entries arrived a step ago, and a step
+ *   costs no launch more than on one GPU), or `seq` itself (the kernel then ends once every peer's
+ *   push of `seq` has arrived).
+ * b200norm_finalize_pushed: the finish as a kernel of its own.
+ * Finishing exchange f = waiting (bounded, 2 s; then B200NORM_ERR_TIMEOUT in the status word and the
+ *   kernel carries on) until the entries of slot f % depth carry f's tag, adding the total_shards
+ *   sums of every column left to right in fp32 and casting to w_dtype.  Same bits on every rank and
+ *   as a single GPU summing the same shards.
  *
- * `seq` starts at 1 and grows by 1 per exchange on all ranks alike.  A rank must finish
- * exchange s before it starts exchange s + depth - 1 (3 <= depth <= 8), which keeps a slot from
- * being overwritten before a slower rank has read it.  Passing seq = 0 makes the kernels number
- * the exchanges themselves from counters kept in `counter` (push and finish each count up from
- * 1): nothing in the launch then changes from step to step, so a captured CUDA graph of the step
- * can be replayed.  inbox, flags and counter (128 bytes) must be zero before the first exchange.
+ * `seq` starts at 1 and grows by 1 per exchange on all ranks alike.  Slot reuse: exchange s + depth
+ * overwrites exchange s in every inbox, so it may start only once every rank has finished s.  A
+ * rank's finish of exchange k proves that every peer has PUSHED k, hence -- by the peer's stream
+ * order -- that the peer has finished whatever it had to finish before pushing k.  Two patterns
+ * keep the slots safe (3 <= depth <= 8; use depth >= 4):
+ *   - finishes fused into later pushes (exchange s finishes s - 1 or s): safe from depth 4 on;
+ *   - finishes launched on their own: every rank finishes exchange s before it starts exchange
+ *     s + depth / 2 (integer division), i.e. at most depth / 2 exchanges are pushed-but-unfinished.
+ * A rank that breaks the rule makes a slower peer's wait run out (the tag it waits for has been
+ * overwritten); it does not make the peer add up another exchange's numbers.
+ * Passing seq = 0 (in `seq` and in finish->seq) makes the kernels number the exchanges themselves
+ * from counters kept in `counter` (pushes and finishes each count up from 1): nothing in the launch
+ * then changes from step to step, so a captured CUDA graph of the step can be replayed; the
+ * caller keeps the slot rule.  inbox and counter (128 bytes) must be zero before the first exchange.
  */
 #define B200NORM_MAX_PEERS 8
 typedef struct b200norm_peers {
   int world, rank, depth, total_shards;
-  size_t inbox_bytes;                   /* size of each rank's inbox */
-  void* inbox[B200NORM_MAX_PEERS];      /* inbox[r]: rank r's inbox as mapped in THIS process */
-  void* flags[B200NORM_MAX_PEERS];      /* flags[r]: rank r's (depth, world) u64 flags, likewise */
+  size_t inbox_bytes;                   /* size of each rank's inbox: a multiple of 16 * depth, at least
+                                           depth * total_shards * slots * N * 8 */
+  void* inbox[B200NORM_MAX_PEERS];      /* inbox[r]: rank r's inbox as mapped in THIS process (16-byte aligned) */
   void* counter;                        /* this rank's own 128 bytes of bookkeeping, zeroed once */
 } b200norm_peers;
+
+/* An exchange to finish: its number (0 = the one after the last finished, by the device-side count),
+ * its shape and where dweight [and dbias] go (either may be NULL). */
+typedef struct b200norm_finish {
+  uint64_t seq;
+  int slots;      /* 1: dweight; 2: dweight and dbias */
+  int w_dtype;
+  int64_t N;
+  void* dw;
+  void* db;
+} b200norm_finish;
 
 B200NORM_API int b200norm_ln_bwd_push(const void* x, int64_t x_row_stride, const void* dy, int64_t dy_row_stride,
                                       const void* w, const float* mean, const float* rstd, void* dx,
                                       int64_t dx_row_stride, int row_shards, void* workspace,
                                       size_t workspace_bytes, int64_t M, int64_t N, int io_dtype, int w_dtype,
-                                      const b200norm_peers* peers, uint64_t seq, void* stream);
+                                      const b200norm_peers* peers, uint64_t seq, const b200norm_finish* finish,
+                                      void* stream);
 B200NORM_API int b200norm_rms_bwd_push(const void* x, int64_t x_row_stride, const void* dy, int64_t dy_row_stride,
                                        const void* w, const float* rstd, void* dx, int64_t dx_row_stride,
                                        int row_shards, void* workspace, size_t workspace_bytes, int64_t M,
                                        int64_t N, int io_dtype, int w_dtype, const b200norm_peers* peers,
-                                       uint64_t seq, void* stream);
+                                       uint64_t seq, const b200norm_finish* finish, void* stream);
 B200NORM_API int b200norm_finalize_pushed(const b200norm_peers* peers, uint64_t seq, int slots, void* dw, void* db,
                                           int64_t N, int w_dtype, void* stream);
 

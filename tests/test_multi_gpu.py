@@ -55,40 +55,79 @@ def _worker(rank, world, port, out):
             (dwr,) = ex.finish(hr, dtype)
             torch.cuda.synchronize()
             res[mode] = (dw, db, dwr, dx, dxr)
-        # the library's own exchange: column reduce fused with the push over NVLink peer memory
-        px = PushExchange(max_n=N, slots=2, total_shards=8, device=device)
-        push_res = []
-        for it in range(6):   # more exchanges than inbox slots, two in flight at a time
-            y, mean, rstd = Fn._layernorm_fwd(x[r0:r1], w, b, eps)
-            dx, h = px.backward_layernorm(x[r0:r1], dy[r0:r1], w, b, mean, rstd, eps)
-            yr, rstd_r = Fn._rmsnorm_fwd(x[r0:r1], w, eps)
-            dxr, hr = px.backward_rmsnorm(x[r0:r1], dy[r0:r1], w, rstd_r, eps)
-            dw, db = px.finish(h, dtype)
-            (dwr,) = px.finish(hr, dtype)
-            push_res.append((dw, db, dwr, dx, dxr))
+        # The library's own exchange: column reduce fused with the push over NVLink peer memory.
+        # Four ways of driving it, each over more exchanges than the inbox has slots:
+        #   "apart"   finishes as kernels of their own, the maximum number of exchanges open (depth // 2)
+        #   "next"    each push kernel finishes the previous exchange (the pipeline the benchmark times)
+        #   "same"    each push kernel finishes its own exchange (waits for every peer's push)
+        #   "counted" as "next" with the exchanges numbered on the device (graph-replayable form)
+        xs, dys = x[r0:r1], dy[r0:r1]
+        push_res = {}
+        for how in ("apart", "next", "same", "counted"):
+            px = PushExchange(max_n=N, slots=2, total_shards=8, device=device, device_numbering=(how == "counted"))
+            got = []
+            prev_ln = prev_rms = None
+            for it in range(6):
+                y, mean, rstd = Fn._layernorm_fwd(xs, w, b, eps)
+                yr, rstd_r = Fn._rmsnorm_fwd(xs, w, eps)
+                if how == "apart":
+                    dx, h = px.backward_layernorm(xs, dys, w, b, mean, rstd, eps)
+                    dxr, hr = px.backward_rmsnorm(xs, dys, w, rstd_r, eps)
+                    dw, db = px.finish(h, dtype)
+                    (dwr,) = px.finish(hr, dtype)
+                    got.append((dw, db, dwr, dx, dxr))
+                elif how == "same":
+                    dx, _, (dw, db) = px.backward_layernorm(xs, dys, w, b, mean, rstd, eps,
+                                                            finish=(PushExchange.SAME, dtype))
+                    dxr, _, (dwr,) = px.backward_rmsnorm(xs, dys, w, rstd_r, eps, finish=(PushExchange.SAME, dtype))
+                    got.append((dw, db, dwr, dx, dxr))
+                else:
+                    # LayerNorm exchange k is finished by the RMSNorm push that follows it, and that RMSNorm
+                    # exchange by the next iteration's LayerNorm push: one open exchange at a time.
+                    if prev_rms is None:
+                        dx, h = px.backward_layernorm(xs, dys, w, b, mean, rstd, eps)
+                    else:
+                        dx, h, (dwr_prev,) = px.backward_layernorm(xs, dys, w, b, mean, rstd, eps,
+                                                                   finish=(prev_rms, dtype))
+                        got[-1] = got[-1][:2] + (dwr_prev,) + got[-1][3:]
+                    dxr, hr, (dw, db) = px.backward_rmsnorm(xs, dys, w, rstd_r, eps, finish=(h, dtype))
+                    got.append((dw, db, None, dx, dxr))
+                    prev_rms = hr
+            if how in ("next", "counted"):
+                (dwr_last,) = px.finish(prev_rms, dtype)
+                got[-1] = got[-1][:2] + (dwr_last,) + got[-1][3:]
+            push_res[how] = got
         torch.cuda.synchronize()
         dist.barrier()
-        if rank == 0:
-            # the single-GPU run of the whole batch with the same 8 row shards
-            y1, mean1, rstd1 = Fn._layernorm_fwd(x, w, b, eps)
-            dx1, dw1, db1 = Fn._layernorm_bwd(x, dy, w, b, mean1, rstd1, eps, row_shards=8)
-            _, rstd1r = Fn._rmsnorm_fwd(x, w, eps)
-            dx1r, dw1r = Fn._rmsnorm_bwd(x, dy, w, rstd1r, eps, row_shards=8)
-            torch.cuda.synchronize()
-            dw, db, dwr, dx, dxr = res["all_gather"]
-            out["gather_bit_exact"] = bool(torch.equal(dw, dw1) and torch.equal(db, db1) and torch.equal(dwr, dw1r))
-            out["dx_bit_exact"] = bool(torch.equal(dx, dx1[r0:r1]) and torch.equal(dxr, dx1r[r0:r1]))
-            out["push_bit_exact"] = all(
+        # Every rank holds the whole batch (same seed), so every rank checks its own results against its own
+        # single-GPU run of the whole batch with the same 8 row shards; the verdicts are combined over ranks.
+        y1, mean1, rstd1 = Fn._layernorm_fwd(x, w, b, eps)
+        dx1, dw1, db1 = Fn._layernorm_bwd(x, dy, w, b, mean1, rstd1, eps, row_shards=8)
+        _, rstd1r = Fn._rmsnorm_fwd(x, w, eps)
+        dx1r, dw1r = Fn._rmsnorm_bwd(x, dy, w, rstd1r, eps, row_shards=8)
+        torch.cuda.synchronize()
+        verdict = {}
+        dw, db, dwr, dx, dxr = res["all_gather"]
+        verdict["gather_bit_exact"] = bool(torch.equal(dw, dw1) and torch.equal(db, db1) and torch.equal(dwr, dw1r))
+        verdict["dx_bit_exact"] = bool(torch.equal(dx, dx1[r0:r1]) and torch.equal(dxr, dx1r[r0:r1]))
+        for how, got in push_res.items():
+            verdict["push_bit_exact_" + how] = all(
                 bool(torch.equal(dw, dw1) and torch.equal(db, db1) and torch.equal(dwr, dw1r) and
                      torch.equal(dx, dx1[r0:r1]) and torch.equal(dxr, dx1r[r0:r1]))
-                for dw, db, dwr, dx, dxr in push_res)
-            from b200norm import _lib
-            out["status"] = _lib.load().b200norm_device_status(0)
-            dw, db, dwr, _, _ = res["all_reduce"]
-            scale = dw1.float().abs().max().item()
-            out["reduce_err"] = max((dw.float() - dw1.float()).abs().max().item(),
-                                    (db.float() - db1.float()).abs().max().item(),
-                                    (dwr.float() - dw1r.float()).abs().max().item()) / scale
+                for dw, db, dwr, dx, dxr in got)
+        from b200norm import _lib
+        verdict["status_clean"] = _lib.load().b200norm_device_status(0) == 0
+        dw, db, dwr, _, _ = res["all_reduce"]
+        scale = dw1.float().abs().max().item()
+        err = max((dw.float() - dw1.float()).abs().max().item(), (db.float() - db1.float()).abs().max().item(),
+                  (dwr.float() - dw1r.float()).abs().max().item()) / scale
+        keys = sorted(verdict)
+        flags = torch.tensor([float(verdict[k]) for k in keys] + [-err], device=device, dtype=torch.float64)
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)       # a check holds only if it holds on every rank
+        if rank == 0:
+            for k, v in zip(keys, flags[:-1].tolist()):
+                out[k] = bool(v)
+            out["reduce_err"] = -flags[-1].item()
     finally:
         dist.destroy_process_group()
 
@@ -103,6 +142,8 @@ def test_sharded_run_reproduces_single_gpu_gradients():
         mp.spawn(_worker, args=(world, _free_port(), out), nprocs=world, join=True)
         assert out["gather_bit_exact"], "all_gather exchange must reproduce the single-GPU dweight/dbias bit for bit"
         assert out["dx_bit_exact"]
-        assert out["push_bit_exact"], "fused push exchange must reproduce the single-GPU dweight/dbias bit for bit"
-        assert out["status"] == 0
+        for how in ("apart", "next", "same", "counted"):
+            assert out["push_bit_exact_" + how], \
+                f"fused push exchange ({how}) must reproduce the single-GPU dweight/dbias bit for bit"
+        assert out["status_clean"], "a bounded wait ran out on some rank"
         assert out["reduce_err"] <= 1e-2      # bf16 parameters: one ulp of the largest gradient

@@ -223,20 +223,10 @@ def test_row_shards_equal_separate_launches_bit_for_bit(rms):
     assert torch.equal(torch.cat(dxs, 0), dx)
 
 
-@pytest.mark.parametrize("rms", [False, True])
-@pytest.mark.parametrize("world", [1, 4])
-def test_fused_push_exchange_emulated_on_one_gpu(rms, world):
-    """The column reduce that pushes shard sums into every rank's inbox, with the ranks emulated as
-    consecutive launches on one GPU (each 'rank' has its own inbox, flags and counter; a flag is
-    always set by an earlier launch before a finish kernel looks at it, so nothing waits).  Every
-    rank's finished dweight / dbias must equal the single-launch 8-shard result bit for bit, over
-    several exchanges that reuse the inbox slots."""
-    import ctypes
-    M, N, S, depth = 8 * 300, 2048, 8, 4
-    slots = 1 if rms else 2
-    lib = _lib.load()
-    inbox_bytes = depth * S * slots * N * 4
-    bufs = [torch.zeros(inbox_bytes + 256 * depth, dtype=torch.uint8, device=DEV) for _ in range(world)]
+def _emulated_peers(world, depth, S, slots, N):
+    """`world` ranks on one GPU: each has its own inbox and counter, all in one address space."""
+    inbox_bytes = depth * S * slots * N * 8          # 8-byte {value, tag} entries
+    bufs = [torch.zeros(inbox_bytes, dtype=torch.uint8, device=DEV) for _ in range(world)]
     counters = [torch.zeros(32, dtype=torch.int32, device=DEV) for _ in range(world)]
     peers = []
     for r in range(world):
@@ -244,24 +234,49 @@ def test_fused_push_exchange_emulated_on_one_gpu(rms, world):
         pr.world, pr.rank, pr.depth, pr.total_shards, pr.inbox_bytes = world, r, depth, S, inbox_bytes
         for q in range(world):
             pr.inbox[q] = bufs[q].data_ptr()
-            pr.flags[q] = bufs[q].data_ptr() + inbox_bytes
         pr.counter = counters[r].data_ptr()
         peers.append(pr)
+    return peers, (bufs, counters)
+
+
+@pytest.mark.parametrize("rms", [False, True])
+@pytest.mark.parametrize("world", [1, 4])
+@pytest.mark.parametrize("fused_finish", [False, True])
+def test_fused_push_exchange_emulated_on_one_gpu(rms, world, fused_finish):
+    """The column reduce that pushes shard sums into every rank's inbox, with the ranks emulated as
+    consecutive launches on one GPU (each 'rank' has its own inbox and counter; an entry is always
+    written by an earlier launch before a finish looks at it, so nothing waits).  Every rank's
+    finished dweight / dbias must equal the single-launch 8-shard result bit for bit, over several
+    exchanges that reuse the inbox slots -- finished by the stand-alone kernel, or (fused_finish) as
+    the second phase of the NEXT exchange's push kernel, with a different row length in between."""
+    import ctypes
+    M, N, S, depth = 8 * 300, 2048, 8, 4
+    slots = 1 if rms else 2
+    lib = _lib.load()
+    peers, keep = _emulated_peers(world, depth, S, slots, N)
     per = M // world
-    for seq in range(1, 7):       # more exchanges than inbox slots
+    pending = None      # (seq, N, expected dw, expected db) of the exchange still to be finished
+    for seq in range(1, 8):       # more exchanges than inbox slots
         if seq == 4:              # an exchange of another shape in between must not disturb the slots
             N = 1024
+        if seq == 6:              # an odd row length: single entries instead of pairs
+            N = 1001
         x, dy, w, b = make_inputs(M, N, "bf16", seed=seq, has_b=not rms)
         xt, dyt, wt, bt = (to_torch(a, "bf16", DEV) for a in (x, dy, w, b))
         if rms:
             _, rstd = Fn._rmsnorm_fwd(xt, wt, 1e-6)
             dx1, dw1 = Fn._rmsnorm_bwd(xt, dyt, wt, rstd, 1e-6, row_shards=S)
+            db1 = None
         else:
             _, mean, rstd = Fn._layernorm_fwd(xt, wt, bt, 1e-6)
             dx1, dw1, db1 = Fn._layernorm_bwd(xt, dyt, wt, bt, mean, rstd, 1e-6, row_shards=S)
+        fused = []
         for r in range(world):
             sl = slice(r * per, (r + 1) * per)
-            push = (ctypes.byref(peers[r]), seq)
+            fin = outs = None
+            if fused_finish and pending is not None:
+                fin, outs = Fn.finish_request(pending[0], slots, pending[1], torch.bfloat16, torch.device(DEV))
+            push = (ctypes.byref(peers[r]), seq, ctypes.byref(fin) if fin is not None else None)
             if rms:
                 dx, _ = Fn._rmsnorm_bwd(xt[sl], dyt[sl], wt, rstd[sl], 1e-6, row_shards=S // world, need_dw=False,
                                         push=push)
@@ -269,17 +284,88 @@ def test_fused_push_exchange_emulated_on_one_gpu(rms, world):
                 dx, _, _ = Fn._layernorm_bwd(xt[sl], dyt[sl], wt, bt, mean[sl], rstd[sl], 1e-6,
                                              row_shards=S // world, need_dw=False, need_db=False, push=push)
             assert torch.equal(dx, dx1[sl])
+            fused.append(outs)
+        if fused_finish:
+            if pending is not None:
+                for r in range(world):
+                    assert torch.equal(fused[r][0], pending[2]), f"rank {r} seq {pending[0]}: dweight differs"
+                    if not rms:
+                        assert torch.equal(fused[r][1], pending[3]), f"rank {r} seq {pending[0]}: dbias differs"
+            pending = (seq, N, dw1, db1)
+            continue
         for r in range(world):
             outs = Fn.finalize_pushed(ctypes.byref(peers[r]), seq, slots, N, torch.bfloat16, torch.device(DEV))
             assert torch.equal(outs[0], dw1), f"rank {r} seq {seq}: dweight differs"
             if not rms:
                 assert torch.equal(outs[1], db1), f"rank {r} seq {seq}: dbias differs"
+    if pending is not None:     # the last exchange of the fused pipeline is closed by the stand-alone kernel
+        for r in range(world):
+            outs = Fn.finalize_pushed(ctypes.byref(peers[r]), pending[0], slots, pending[1], torch.bfloat16,
+                                      torch.device(DEV))
+            assert torch.equal(outs[0], pending[2])
     torch.cuda.synchronize()
     with torch.cuda.device(0):
         assert lib.b200norm_device_status(0) == 0
 
 
-def test_finish_kernel_gives_up_on_a_flag_nobody_sets():
+@pytest.mark.parametrize("device_numbering", [False, True])
+def test_push_exchange_finishing_its_own_exchange_on_one_rank(device_numbering):
+    """world = 1 through the PushExchange class: every backward finishes the exchange it pushes in the
+    same kernel (the CTAs wait for entries other CTAs of the grid write); with device_numbering the
+    kernels count the exchanges themselves.  Bit-identical to the plain backward with 8 row shards."""
+    from b200norm.parallel import PushExchange
+    M, N = 8 * 200, 4096
+    px = PushExchange(max_n=N, slots=2, total_shards=8, device=torch.device(DEV), device_numbering=device_numbering)
+    for it in range(6):
+        x, dy, w, b = make_inputs(M, N, "bf16", seed=40 + it)
+        xt, dyt, wt, bt = (to_torch(a, "bf16", DEV) for a in (x, dy, w, b))
+        _, mean, rstd = Fn._layernorm_fwd(xt, wt, bt, 1e-6)
+        dx1, dw1, db1 = Fn._layernorm_bwd(xt, dyt, wt, bt, mean, rstd, 1e-6, row_shards=8)
+        dx, _, (dw, db) = px.backward_layernorm(xt, dyt, wt, bt, mean, rstd, 1e-6,
+                                                finish=(PushExchange.SAME, torch.bfloat16))
+        assert torch.equal(dx, dx1) and torch.equal(dw, dw1) and torch.equal(db, db1)
+        _, rstd = Fn._rmsnorm_fwd(xt, wt, 1e-6)
+        dx1, dw1 = Fn._rmsnorm_bwd(xt, dyt, wt, rstd, 1e-6, row_shards=8)
+        dx, _, (dw,) = px.backward_rmsnorm(xt, dyt, wt, rstd, 1e-6, finish=(PushExchange.SAME, torch.bfloat16))
+        assert torch.equal(dx, dx1) and torch.equal(dw, dw1)
+    torch.cuda.synchronize()
+    with torch.cuda.device(0):
+        assert _lib.load().b200norm_device_status(0) == 0
+
+
+def test_push_exchange_refuses_more_open_exchanges_than_the_slots_allow():
+    """Slot reuse: at depth 4 at most two exchanges may be pushed-but-unfinished when another starts
+    (finish s before starting s + depth // 2).  p1 p2 [p3 refused] f1 p3 [p4 refused] f2 p4 -- and
+    every finished exchange is still bit-exact at that maximum."""
+    from b200norm.parallel import PushExchange
+    M, N = 8 * 64, 1024
+    px = PushExchange(max_n=N, slots=1, total_shards=8, depth=4, device=torch.device(DEV))
+    x, dy, w, _ = make_inputs(M, N, "bf16", seed=3, has_b=False)
+    xt, dyt, wt = (to_torch(a, "bf16", DEV) for a in (x, dy, w))
+    _, rstd = Fn._rmsnorm_fwd(xt, wt, 1e-6)
+    _, dw1 = Fn._rmsnorm_bwd(xt, dyt, wt, rstd, 1e-6, row_shards=8)
+    push = lambda: px.backward_rmsnorm(xt, dyt, wt, rstd, 1e-6)[1]
+    h1, h2 = push(), push()
+    with pytest.raises(RuntimeError, match="too many exchanges in flight"):
+        push()
+    (dw,) = px.finish(h1, torch.bfloat16)
+    assert torch.equal(dw, dw1)
+    h3 = push()
+    with pytest.raises(RuntimeError, match="too many exchanges in flight"):
+        push()
+    (dw,) = px.finish(h2, torch.bfloat16)
+    assert torch.equal(dw, dw1)
+    # a finish that rides in the call itself counts: h3 is open, h4 is pushed while finishing h3
+    _, h4, (dw,) = px.backward_rmsnorm(xt, dyt, wt, rstd, 1e-6, finish=(h3, torch.bfloat16))
+    assert torch.equal(dw, dw1)
+    (dw,) = px.finish(h4, torch.bfloat16)
+    assert torch.equal(dw, dw1)
+    torch.cuda.synchronize()
+    with torch.cuda.device(0):
+        assert _lib.load().b200norm_device_status(0) == 0
+
+
+def test_finish_kernel_gives_up_on_entries_nobody_writes():
     """A bounded wait that runs out: the finish kernel is asked for an exchange that no rank has
     pushed.  It must return (after its 2 s limit), leave the context usable and raise the device
     status word -- the host-visible form of a peer that never arrived."""
@@ -287,12 +373,7 @@ def test_finish_kernel_gives_up_on_a_flag_nobody_sets():
     import time
     N, depth, S = 256, 4, 8
     lib = _lib.load()
-    inbox_bytes = depth * S * 1 * N * 4
-    buf = torch.zeros(inbox_bytes + 256 * depth, dtype=torch.uint8, device=DEV)
-    counter = torch.zeros(32, dtype=torch.int32, device=DEV)
-    pr = _lib.Peers()
-    pr.world, pr.rank, pr.depth, pr.total_shards, pr.inbox_bytes = 1, 0, depth, S, inbox_bytes
-    pr.inbox[0], pr.flags[0], pr.counter = buf.data_ptr(), buf.data_ptr() + inbox_bytes, counter.data_ptr()
+    (pr,), keep = _emulated_peers(1, depth, S, 1, N)
     with torch.cuda.device(0):
         assert lib.b200norm_device_status(1) == 0
         t0 = time.time()
@@ -308,6 +389,30 @@ def test_finish_kernel_gives_up_on_a_flag_nobody_sets():
         y, _ = Fn._rmsnorm_fwd(x, None, 1e-6)
         torch.cuda.synchronize()
         assert torch.isfinite(y).all()
+
+
+def test_an_overwritten_inbox_slot_makes_the_late_finish_time_out_instead_of_adding_wrong_sums():
+    """What the exchange tags buy: a finish of exchange s that comes after exchange s + depth has
+    overwritten the slot does not see s's tag any more, waits out its limit and raises the status
+    word -- it never adds up the other exchange's numbers as if they were its own."""
+    import ctypes
+    N, depth, S = 256, 4, 8
+    lib = _lib.load()
+    (pr,), keep = _emulated_peers(1, depth, S, 1, N)
+    x = torch.randn(8 * 16, N, device=DEV)
+    w = torch.ones(N, device=DEV)
+    _, rstd = Fn._rmsnorm_fwd(x, w, 1e-6)
+    with torch.cuda.device(0):
+        assert lib.b200norm_device_status(1) == 0
+        for seq in (1, 1 + depth):      # the same slot twice, nothing finished in between
+            Fn._rmsnorm_bwd(x, torch.randn_like(x), w, rstd, 1e-6, row_shards=S, need_dw=False,
+                            push=(ctypes.byref(pr), seq, None))
+        Fn.finalize_pushed(ctypes.byref(pr), 1, 1, N, torch.float32, torch.device(DEV))
+        torch.cuda.synchronize()
+        assert lib.b200norm_device_status(1) == _lib.ERR_TIMEOUT
+        (dw,) = Fn.finalize_pushed(ctypes.byref(pr), 1 + depth, 1, N, torch.float32, torch.device(DEV))
+        torch.cuda.synchronize()
+        assert lib.b200norm_device_status(0) == 0 and torch.isfinite(dw).all()
 
 
 def test_outputs_do_not_write_out_of_bounds():

@@ -18,7 +18,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 from b200norm import _lib
-from helpers import TOL, assert_parity, to_numpy
+from helpers import TOL, assert_parity, oracle_all, to_numpy
 
 DEV = "cuda:0"
 CODE = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
@@ -70,6 +70,67 @@ def test_static_scratch_matches_workspace_entry_point_two_calls_in_a_row(dtype, 
             assert_parity(to_numpy(dw), to_numpy(want_dw), tol, f"call {call + 1}: dw")
             # same kernels, same launch plan, same fixed-order reduction: the results are in fact identical
             assert torch.equal(dx, want_dx) and torch.equal(dw, want_dw)
+
+
+def _check_against_oracle(x, dy, w, rstd, dx, dw, what):
+    """dx and dweight against the CPU oracle (fp64 accumulation, rounded to the storage type)."""
+    name = NAME[x.dtype]
+    ref = oracle_all(to_numpy(x), to_numpy(dy), to_numpy(w), None, 1e-6, rms=True, dtype=name, acc64=True)
+    assert_parity(to_numpy(dx), ref["dx"], TOL[name], what + ": dx vs oracle")
+    assert_parity(to_numpy(dw), ref["dw"], TOL[name], what + ": dw vs oracle")
+
+
+@pytest.mark.parametrize("dtype,M,N", [(torch.bfloat16, 300, 4096), (torch.float32, 129, 1000)])
+def test_static_scratch_result_matches_the_oracle(dtype, M, N):
+    lib = _lib.load()
+    with torch.cuda.device(0):
+        x, dy, w, rstd = _inputs(M, N, dtype, 21)
+        rc, dx, dw = _static(lib, x, dy, w, rstd)
+        _lib.check(rc)
+        torch.cuda.synchronize()
+        _check_against_oracle(x, dy, w, rstd, dx, dw, "static")
+
+
+# One kernel instantiation serves a range of row lengths, each with its own dynamic shared-memory
+# size, and the allowance a kernel has been granted is per device -- so the two entry points must
+# keep ONE record of it.  (long, short) pairs below fall on the same instantiation.
+@pytest.mark.parametrize("long_n,short_n", [(4096, 3200), (16384, 12800)])
+@pytest.mark.parametrize("static_first", [False, True])
+def test_a_shorter_row_on_one_entry_point_leaves_the_other_entry_points_longer_row_launchable(long_n, short_n,
+                                                                                                 static_first):
+    lib = _lib.load()
+    dtype, M = torch.bfloat16, 296
+    with torch.cuda.device(0):
+        long_in = _inputs(M, long_n, dtype, 31)
+        short_in = _inputs(M, short_n, dtype, 32)
+
+        def workspace(inp, what):
+            dx, dw = _with_workspace(lib, *inp)
+            torch.cuda.synchronize()
+            _check_against_oracle(*inp, dx, dw, what)
+
+        def static(inp, what, need_dw=True):
+            x, dy, w, rstd = inp
+            rc, dx, dw = _static(lib, x, dy, w, rstd)
+            _lib.check(rc)
+            torch.cuda.synchronize()
+            _check_against_oracle(*inp, dx, dw, what)
+
+        # N = 16384 needs more partial rows than the built-in scratch holds, so the static side of that
+        # pair always takes the shorter row; the other pair is run in both roles.
+        if static_first and long_n * 148 * 4 <= 8 << 20:
+            static(long_in, "static, long row")
+            workspace(short_in, "workspace, short row")
+            static(long_in, "static, long row again")
+        elif static_first:
+            static(short_in, "static, short row")
+            workspace(long_in, "workspace, long row")
+            static(short_in, "static, short row again")
+            workspace(long_in, "workspace, long row again")
+        else:
+            workspace(long_in, "workspace, long row")
+            static(short_in, "static, short row")
+            workspace(long_in, "workspace, long row again")
 
 
 def test_shapes_beyond_the_built_in_scratch_are_refused_with_a_clear_error():

@@ -29,11 +29,15 @@ MAX_PEERS = 8
 class Peers(ctypes.Structure):
     """struct b200norm_peers: where the fused column reduce pushes shard sums (see b200norm.h)."""
     _fields_ = [("world", _int), ("rank", _int), ("depth", _int), ("total_shards", _int),
-                ("inbox_bytes", _sz), ("inbox", _vp * MAX_PEERS), ("flags", _vp * MAX_PEERS),
-                ("counter", _vp)]
+                ("inbox_bytes", _sz), ("inbox", _vp * MAX_PEERS), ("counter", _vp)]
 
 
-_pp, _u64 = _c.POINTER(Peers), _c.c_uint64
+class Finish(ctypes.Structure):
+    """struct b200norm_finish: an exchange for a push kernel to finish as its second phase."""
+    _fields_ = [("seq", _c.c_uint64), ("slots", _int), ("w_dtype", _int), ("N", _i64), ("dw", _vp), ("db", _vp)]
+
+
+_pp, _fp, _u64 = _c.POINTER(Peers), _c.POINTER(Finish), _c.c_uint64
 
 # name -> (restype, argtypes): every symbol include/b200norm.h declares.
 SIGNATURES = {
@@ -64,9 +68,9 @@ SIGNATURES = {
     "b200norm_rms_act_bwd": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _int, _vp, _sz, _i64, _i64,
                                     _int, _int, _int, _vp]),
     "b200norm_ln_bwd_push": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _int, _vp, _sz, _i64, _i64, _int,
-                                    _int, _pp, _u64, _vp]),
+                                    _int, _pp, _u64, _fp, _vp]),
     "b200norm_rms_bwd_push": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _int, _vp, _sz, _i64, _i64, _int, _int,
-                                     _pp, _u64, _vp]),
+                                     _pp, _u64, _fp, _vp]),
     "b200norm_finalize_pushed": (_int, [_pp, _u64, _int, _vp, _vp, _i64, _int, _vp]),
     "b200norm_rms_bwd_static": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _int, _int, _vp]),
 }

@@ -170,18 +170,19 @@ def _bwd_common(op, x, dout, weight, bias, mean, rstd, row_shards, want_group_su
             ws_bytes = _workspace_bytes(lib, x.device.index, M, N, _code(x, "input"), row_shards)
             ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=x.device)
         stream = _raw_stream(x.device.index)
-        if push is not None:  # (Peers struct, sequence number): shard sums go to every rank's inbox
-            peers, seq = push
+        if push is not None:  # (Peers, sequence number[, Finish]): shard sums go to every rank's inbox
+            peers, seq = push[0], push[1]
+            fin = push[2] if len(push) > 2 else None
             if op == "ln":
                 status = lib.b200norm_ln_bwd_push(
                     x.data_ptr(), _row_stride(x), dout.data_ptr(), _row_stride(dout), _ptr(weight),
                     mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(), N, row_shards, _ptr(ws), ws_bytes, M, N,
-                    _code(x, "input"), wcode, peers, seq, stream)
+                    _code(x, "input"), wcode, peers, seq, fin, stream)
             else:
                 status = lib.b200norm_rms_bwd_push(
                     x.data_ptr(), _row_stride(x), dout.data_ptr(), _row_stride(dout), _ptr(weight),
                     rstd.data_ptr(), dx.data_ptr(), N, row_shards, _ptr(ws), ws_bytes, M, N,
-                    _code(x, "input"), wcode, peers, seq, stream)
+                    _code(x, "input"), wcode, peers, seq, fin, stream)
         elif op == "ln":
             status = lib.b200norm_ln_bwd(
                 x.data_ptr(), _row_stride(x), dout.data_ptr(), _row_stride(dout), _ptr(weight),
@@ -201,8 +202,9 @@ def _layernorm_bwd(x, dout, weight, bias, mean, rstd, eps, *, row_shards=1, grou
     """LayerNorm backward; returns (dx, dweight, dbias), the last two in the parameters' dtype
     (None for a missing parameter).  With ``group_sums=True`` a fourth value is returned: the
     fp32 (row_shards, 2, N) dweight/dbias sums per row shard, for a multi-GPU exchange.
-    ``eps`` is accepted and unused, as in the reference.  ``push=(peers, seq)`` sends the shard sums
-    to every rank's inbox instead (b200norm_ln_bwd_push); pass need_dw=need_db=False with it."""
+    ``eps`` is accepted and unused, as in the reference.  ``push=(peers, seq[, finish])`` sends the shard
+    sums to every rank's inbox instead (b200norm_ln_bwd_push; `finish` = a pointer to a _lib.Finish naming
+    an exchange for the same kernel to finish); pass need_dw=need_db=False with it."""
     dx, dw, db, gs = _bwd_common("ln", x, dout, weight, bias, mean, rstd, row_shards, group_sums,
                                  need_dw, need_db, push)
     return (dx, dw, db, gs) if group_sums else (dx, dw, db)
@@ -230,6 +232,17 @@ def finalize_dwdb(group_sums: torch.Tensor, w_dtype: torch.dtype):
             group_sums.data_ptr(), groups, slots, outs[0].data_ptr(),
             outs[1].data_ptr() if slots == 2 else None, N, code, _raw_stream(group_sums.device.index)))
     return tuple(outs)
+
+
+def finish_request(seq, slots, N, w_dtype, device):
+    """-> (_lib.Finish, outs): a request for a push kernel to finish exchange `seq` as its second phase,
+    and the freshly allocated dweight[, dbias] it will fill.  Keep both alive until the call returns."""
+    outs = tuple(torch.empty((N,), dtype=w_dtype, device=device) for _ in range(slots))
+    fin = _lib.Finish()
+    fin.seq, fin.slots, fin.w_dtype, fin.N = seq, slots, _DTYPE_CODE[w_dtype], N
+    fin.dw = outs[0].data_ptr()
+    fin.db = outs[1].data_ptr() if slots == 2 else None
+    return fin, outs
 
 
 def finalize_pushed(peers, seq, slots, N, w_dtype, device):

@@ -11,9 +11,9 @@ data-parallel layer added on top of its `_layernorm_bwd` / `_rmsnorm_bwd`
 (TritonHub/Normalization/layernorm.py:155-209, rmsnorm.py:124-167).
 
 Three exchange paths:
-  PushExchange  the library's own: the backward's column-reduce kernel stores its shard sums
-                straight into every rank's inbox over NVLink peer memory and raises a flag; a
-                later finish kernel adds them left to right.  No collective-library kernel has to
+  PushExchange  the library's own: the backward's column-reduce kernel stores its shard sums,
+                each tagged with the exchange number, straight into every rank's inbox over NVLink
+                peer memory; a later kernel (or the next exchange's) adds them left to right.  No collective-library kernel has to
                 be co-resident with the persistent forward / backward grids, and the result is
                 bit-identical across ranks, runs and GPU counts.  This is the default.
   GradExchange  over torch.distributed collectives, in one of two modes:
@@ -137,14 +137,30 @@ def sharded_rmsnorm_bwd(x, dout, weight, rstd, eps, exchange: GradExchange):
 class PushExchange:
     """dweight / dbias exchange fused into the backward's column reduce (b200norm_*_bwd_push).
 
-    Each rank owns an inbox (depth, total_shards, slots, max_n) fp32 plus a flag array in
-    symmetric memory (torch.distributed._symmetric_memory: CUDA VMM allocations mapped into every
-    rank of the group).  `backward_*` launches the backward whose column reduce pushes this
-    rank's shard sums to all ranks; `finish` launches the kernel that waits (on the GPU, bounded)
-    for everyone's flags and adds the shards left to right.  Nothing blocks the host.
+    Each rank owns an inbox (depth, total_shards, slots, max_n) of 8-byte {fp32 value, exchange tag}
+    entries in symmetric memory (torch.distributed._symmetric_memory: CUDA VMM allocations mapped into
+    every rank of the group).  `backward_*` launches the backward whose column reduce stores this
+    rank's shard sums into all ranks' inboxes; finishing an exchange waits (on the GPU, bounded) for
+    everyone's entries and adds the shards left to right.  Nothing blocks the host.
 
-    A rank may run at most `depth - 2` exchanges ahead of its oldest unfinished one.
+    An exchange is finished either by `finish(handle, dtype)` -- a kernel of its own -- or inside a
+    later `backward_*(..., finish=(handle, dtype))` call, whose push kernel does it as a second phase:
+    the usual pipeline finishes exchange s - 1 in exchange s, so a step costs no launch more than on
+    one GPU.  `finish=(SAME, dtype)` finishes the exchange being pushed in its own kernel.
+
+    Slot reuse: exchange s + depth overwrites the inbox slot of exchange s on every peer, so a rank
+    may start it only once every peer has finished s.  All a rank learns from its own finish of
+    exchange k is that every peer has PUSHED k -- hence, by the peer's stream order, that the peer
+    has finished whatever it had to finish before pushing k.  With the rule "finish s before starting
+    s + W" on every rank, starting s + depth implies own finish of s + depth - W, implies the peers
+    pushed s + depth - W, implies they finished s + depth - 2W: safe exactly when W <= depth / 2.  So
+    at most depth // 2 exchanges may be open (pushed, not finished) when another starts; `_next`
+    enforces it, counting an exchange whose finish rides in the very call as finished.  (A rank that
+    broke the rule would make a slower peer's wait run out, not hand it wrong sums: the tags differ.)
+    With device_numbering the caller keeps the same rule.
     """
+
+    SAME = "same"  # finish=(PushExchange.SAME, dtype): finish the exchange this call pushes
 
     def __init__(self, max_n: int, slots: int = 2, group: Optional[dist.ProcessGroup] = None,
                  total_shards: Optional[int] = None, depth: int = 4, device: Optional[torch.device] = None,
@@ -162,65 +178,93 @@ class PushExchange:
         self.local_shards = local_row_shards(self.world, total_shards)
         self.total_shards, self.depth, self.slots, self.max_n = total_shards, depth, slots, max_n
         self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
-        self.inbox_bytes = depth * total_shards * slots * max_n * 4
-        flag_bytes = (depth * max(self.world, 1) * 8 + 255) // 256 * 256
+        self.inbox_bytes = depth * ((total_shards * slots * max_n * 8 + 15) // 16 * 16)
         # device_numbering: the kernels count the exchanges themselves (seq = 0 in the ABI), so that a
         # CUDA graph holding backward_* / finish calls can be replayed; the caller then keeps the
-        # "at most depth - 2 ahead" rule itself.
+        # "at most depth // 2 open exchanges" rule itself.
         self.device_numbering = device_numbering
         self._seq = 0
         self._oldest_open = 1
         self.counter = torch.zeros(32, dtype=torch.int32, device=self.device)  # 128 bytes of bookkeeping
         if self.world == 1:
-            self._buf = torch.zeros(self.inbox_bytes + flag_bytes, dtype=torch.uint8, device=self.device)
+            self._buf = torch.zeros(self.inbox_bytes, dtype=torch.uint8, device=self.device)
             bases = [self._buf.data_ptr()]
         else:
             import torch.distributed._symmetric_memory as symm_mem
-            self._buf = symm_mem.empty(self.inbox_bytes + flag_bytes, dtype=torch.uint8, device=self.device)
+            self._buf = symm_mem.empty(self.inbox_bytes, dtype=torch.uint8, device=self.device)
             self._buf.zero_()
             self._hdl = symm_mem.rendezvous(self._buf, self.group)
             bases = [int(p) for p in self._hdl.buffer_ptrs]
             torch.cuda.synchronize(self.device)
-            dist.barrier(group=self.group)  # every inbox and flag array is zero before anyone pushes
+            dist.barrier(group=self.group)  # every inbox is zero before anyone pushes
         self.peers = _lib.Peers()
         self.peers.world, self.peers.rank = self.world, self.rank
         self.peers.depth, self.peers.total_shards = depth, total_shards
         self.peers.inbox_bytes = self.inbox_bytes
         for r in range(self.world):
             self.peers.inbox[r] = bases[r]
-            self.peers.flags[r] = bases[r] + self.inbox_bytes
         self.peers.counter = self.counter.data_ptr()
 
-    def _next(self, slots, N):
+    def _next(self, slots, N, finishing=None):
+        """Number of the exchange about to be pushed.  `finishing`: the exchange the same call finishes."""
         if N > self.max_n or slots > self.slots:
             raise ValueError(f"exchange of {slots} x {N} exceeds this PushExchange ({self.slots} x {self.max_n})")
         if self.device_numbering:
             return 0
-        if self._seq + 1 - self._oldest_open > self.depth - 2:
-            raise RuntimeError("too many exchanges in flight: finish() an older one first")
+        oldest = self._oldest_open
+        if finishing is not None and finishing == oldest:
+            oldest += 1
+        if self._seq + 1 - oldest >= self.depth // 2:
+            raise RuntimeError(f"too many exchanges in flight (at most {self.depth // 2} open at depth "
+                               f"{self.depth}): finish the oldest one first")
         self._seq += 1
         return self._seq
 
-    def backward_layernorm(self, x, dout, weight, bias, mean, rstd, eps):
-        """This rank's rows: returns (dx, handle); finish(handle, dtype) yields (dweight, dbias)."""
-        N = x.shape[-1]
-        seq = self._next(2, N)
-        dx, _, _ = Fn._layernorm_bwd(x, dout, weight, bias, mean, rstd, eps, row_shards=self.local_shards,
-                                     need_dw=False, need_db=False, push=(ctypes_ref(self.peers), seq))
-        return dx, (seq, 2, N)
+    def _finish_arg(self, finish, slots, N):
+        """-> (exchange number being finished or None, Finish struct or None, outs, (slots, N) of it)."""
+        if finish is None:
+            return None, None, None
+        handle, w_dtype = finish
+        if isinstance(handle, str) and handle == self.SAME:
+            fseq, fslots, fn = (0 if self.device_numbering else self._seq + 1), slots, N
+        else:
+            fseq, fslots, fn = handle
+        fin, outs = Fn.finish_request(fseq, fslots, fn, w_dtype, self.device)
+        return fseq, fin, outs
 
-    def backward_rmsnorm(self, x, dout, weight, rstd, eps):
-        """RMSNorm twin; finish yields (dweight,)."""
+    def _done(self, fseq):
+        if fseq:
+            self._oldest_open = max(self._oldest_open, fseq + 1)
+
+    def backward_layernorm(self, x, dout, weight, bias, mean, rstd, eps, finish=None):
+        """This rank's rows: returns (dx, handle); finish(handle, dtype) yields (dweight, dbias).
+        With finish=(older handle | SAME, dtype) the call also finishes that exchange and returns
+        (dx, handle, grads of the finished exchange)."""
         N = x.shape[-1]
-        seq = self._next(1, N)
+        fseq, fin, outs = self._finish_arg(finish, 2, N)
+        same = finish is not None and isinstance(finish[0], str)
+        seq = self._next(2, N, None if same else fseq)
+        dx, _, _ = Fn._layernorm_bwd(x, dout, weight, bias, mean, rstd, eps, row_shards=self.local_shards,
+                                     need_dw=False, need_db=False,
+                                     push=(ctypes_ref(self.peers), seq, ctypes_ref(fin) if fin is not None else None))
+        self._done(seq if same else fseq)
+        return (dx, (seq, 2, N)) if finish is None else (dx, (seq, 2, N), outs)
+
+    def backward_rmsnorm(self, x, dout, weight, rstd, eps, finish=None):
+        """RMSNorm twin; a finished RMSNorm exchange yields (dweight,)."""
+        N = x.shape[-1]
+        fseq, fin, outs = self._finish_arg(finish, 1, N)
+        same = finish is not None and isinstance(finish[0], str)
+        seq = self._next(1, N, None if same else fseq)
         dx, _ = Fn._rmsnorm_bwd(x, dout, weight, rstd, eps, row_shards=self.local_shards, need_dw=False,
-                                push=(ctypes_ref(self.peers), seq))
-        return dx, (seq, 1, N)
+                                push=(ctypes_ref(self.peers), seq, ctypes_ref(fin) if fin is not None else None))
+        self._done(seq if same else fseq)
+        return (dx, (seq, 1, N)) if finish is None else (dx, (seq, 1, N), outs)
 
     def finish(self, handle, w_dtype: torch.dtype):
         seq, slots, N = handle
         out = Fn.finalize_pushed(ctypes_ref(self.peers), seq, slots, N, w_dtype, self.device)
-        self._oldest_open = max(self._oldest_open, seq + 1)
+        self._done(seq)
         return out
 
 

@@ -38,19 +38,26 @@ int fail(int code, const char* fmt, ...) {
 }
 
 struct DeviceState {
+  // Launch planning: SM count, occupancies, shared-memory allowances.  Set up without allocating
+  // anything, and shared by every entry point -- a kernel's shared-memory allowance is a property
+  // of the device, so there must be exactly one record of it per device.
   std::once_flag once;
   cudaError_t init_err = cudaSuccess;
   int sm_count = 0;
-  int* status_host = nullptr;  // pinned, mapped: kernels report a timed-out wait here
-  int* status_dev = nullptr;
   std::mutex mu;
   std::unordered_map<unsigned long long, int> occupancy;  // (kernel, dyn smem) -> CTAs per SM
   std::unordered_map<const void*, size_t> smem_limit;     // kernel -> dynamic shared memory it has been allowed
+  // Status word: pinned, mapped host memory where kernels report a timed-out wait.  Allocated by the
+  // first call of an entry point that reports through it (never by b200norm_rms_bwd_static).
+  std::once_flag status_once;
+  cudaError_t status_err = cudaSuccess;
+  int* status_host = nullptr;
+  int* status_dev = nullptr;
 };
 DeviceState g_dev[kMaxDevices];
 
-// Per-device set-up, run by the first call on each device.
-int device_state(DeviceState** out) {
+// The launch-planning part of the current device's state; allocates nothing.
+int device_caches(DeviceState** out) {
   int d = -1;
   cudaError_t e = cudaGetDevice(&d);
   if (e != cudaSuccess) return fail(B200NORM_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
@@ -58,15 +65,26 @@ int device_state(DeviceState** out) {
   DeviceState& s = g_dev[d];
   std::call_once(s.once, [&]() {
     s.init_err = cudaDeviceGetAttribute(&s.sm_count, cudaDevAttrMultiProcessorCount, d);
-    if (s.init_err != cudaSuccess) return;
-    s.init_err = cudaHostAlloc(reinterpret_cast<void**>(&s.status_host), 64, cudaHostAllocMapped);
-    if (s.init_err != cudaSuccess) return;
-    std::memset(s.status_host, 0, 64);
-    s.init_err = cudaHostGetDevicePointer(reinterpret_cast<void**>(&s.status_dev), s.status_host, 0);
   });
   if (s.init_err != cudaSuccess)
     return fail(B200NORM_ERR_CUDA, "device set-up: %s", cudaGetErrorString(s.init_err));
   *out = &s;
+  return B200NORM_OK;
+}
+
+// Per-device set-up, run by the first call on each device: the above plus the status word.
+int device_state(DeviceState** out) {
+  DeviceState* s = nullptr;
+  if (int rc = device_caches(&s)) return rc;
+  std::call_once(s->status_once, [&]() {
+    s->status_err = cudaHostAlloc(reinterpret_cast<void**>(&s->status_host), 64, cudaHostAllocMapped);
+    if (s->status_err != cudaSuccess) return;
+    std::memset(s->status_host, 0, 64);
+    s->status_err = cudaHostGetDevicePointer(reinterpret_cast<void**>(&s->status_dev), s->status_host, 0);
+  });
+  if (s->status_err != cudaSuccess)
+    return fail(B200NORM_ERR_CUDA, "device set-up: %s", cudaGetErrorString(s->status_err));
+  *out = s;
   return B200NORM_OK;
 }
 
@@ -132,6 +150,20 @@ const DTypeKernels* kernels_for(int dtype, int act = 0) {
 
 bool valid_act(int act) { return act >= B200NORM_ACT_NONE && act <= B200NORM_ACT_GELU_TANH; }
 
+// Tuning builds only (-DB200NORM_TUNING, which the shipped library is not built with): an environment
+// variable, read once, that overrides a launch decision -- the index of the table entry to use
+// whenever it can hold the row (B200NORM_FORCE_FWD / _BWD / _SOFTMAX / _PNORM), or B200NORM_PDL=0 to
+// launch without programmatic dependent launch.  Without the flag these return `fallback`.
+int tuning_env(const char* name, int fallback) {
+#ifdef B200NORM_TUNING
+  const char* v = std::getenv(name);
+  return v != nullptr ? std::atoi(v) : fallback;
+#else
+  (void)name;
+  return fallback;
+#endif
+}
+
 constexpr size_t kMaxSmemPerCta = 227 * 1024;  // opt-in dynamic + static shared memory of one sm_100 CTA
 
 bool valid_dtype(int d) { return d >= B200NORM_F32 && d <= B200NORM_F64; }
@@ -155,9 +187,7 @@ size_t bwd_smem_bytes(const PacketKernel& pk, int64_t N, int es, int act) {
 // shared memory fits), or null.
 const PacketKernel* pick(const PacketKernel* tab, int n, int64_t V, bool bwd = false, int64_t N = 0, int es = 0,
                          int act = 0) {
-  // Tuning aid: B200NORM_FORCE_FWD / B200NORM_FORCE_BWD = index of the table entry to use when it can hold the row.
-  static const int forced[2] = {std::getenv("B200NORM_FORCE_FWD") ? std::atoi(std::getenv("B200NORM_FORCE_FWD")) : -1,
-                                std::getenv("B200NORM_FORCE_BWD") ? std::atoi(std::getenv("B200NORM_FORCE_BWD")) : -1};
+  static const int forced[2] = {tuning_env("B200NORM_FORCE_FWD", -1), tuning_env("B200NORM_FORCE_BWD", -1)};
   const int f = forced[bwd ? 1 : 0];
   if (f >= 0 && f < n && tab[f].capacity() >= V && V % tab[f].cluster == 0) return &tab[f];
   for (int i = 0; i < n; ++i) {
@@ -174,10 +204,7 @@ int launch(const void* fn, dim3 grid, dim3 block, size_t smem, void* params, cud
            int cluster = 1) {
   void* args[1] = {params};
   cudaError_t e;
-  static const bool pdl_enabled = []() {  // B200NORM_PDL=0 turns programmatic dependent launch off (A/B timing)
-    const char* v = std::getenv("B200NORM_PDL");
-    return !(v != nullptr && v[0] == '0');
-  }();
+  static const bool pdl_enabled = tuning_env("B200NORM_PDL", 1) != 0;
   if ((pdl && pdl_enabled) || cluster > 1) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -306,34 +333,48 @@ int check_peers(const b200norm_peers* peers, int slots, int64_t N, int row_shard
   if (row_shards >= 1 && peers->world * row_shards != peers->total_shards)
     return fail(B200NORM_ERR_ARG, "peers: world %d x row_shards %d != total_shards %d", peers->world, row_shards,
                 peers->total_shards);
-  // each of the `depth` slots is inbox_bytes / depth and must hold (total_shards, slots, N) fp32
-  const size_t need = static_cast<size_t>(peers->depth) * peers->total_shards * slots * N * sizeof(float);
-  if (need > peers->inbox_bytes || peers->inbox_bytes % (sizeof(float) * peers->depth) != 0)
-    return fail(B200NORM_ERR_ARG, "peers: inbox holds %zu bytes, this exchange needs %zu", peers->inbox_bytes, need);
+  // each of the `depth` slots is inbox_bytes / depth and must hold (total_shards, slots, N) 8-byte entries
+  const size_t need = static_cast<size_t>(peers->depth) * peers->total_shards * slots * N * 8;
+  if (need > peers->inbox_bytes || peers->inbox_bytes % (16 * static_cast<size_t>(peers->depth)) != 0)
+    return fail(B200NORM_ERR_ARG, "peers: inbox holds %zu bytes (must be a multiple of 16 x depth), this exchange needs %zu",
+                peers->inbox_bytes, need);
   if (peers->counter == nullptr) return fail(B200NORM_ERR_ARG, "peers: null counter");
   for (int r = 0; r < peers->world; ++r)
-    if (peers->inbox[r] == nullptr || peers->flags[r] == nullptr)
-      return fail(B200NORM_ERR_ARG, "peers: null inbox / flags for rank %d", r);
+    if (peers->inbox[r] == nullptr || (reinterpret_cast<uintptr_t>(peers->inbox[r]) & 15u) != 0)
+      return fail(B200NORM_ERR_ARG, "peers: null or misaligned inbox for rank %d", r);
   return B200NORM_OK;
 }
 
 PeerTargets peer_targets(const b200norm_peers* peers) {
   PeerTargets t;
-  for (int r = 0; r < kMaxPeers; ++r) {
-    t.inbox[r] = (r < peers->world) ? static_cast<float*>(peers->inbox[r]) : nullptr;
-    t.flags[r] = (r < peers->world) ? static_cast<unsigned long long*>(peers->flags[r]) : nullptr;
-  }
+  for (int r = 0; r < kMaxPeers; ++r)
+    t.inbox[r] = (r < peers->world) ? static_cast<unsigned char*>(peers->inbox[r]) : nullptr;
   t.local = static_cast<LocalState*>(peers->counter);
   t.world = peers->world; t.rank = peers->rank; t.depth = peers->depth; t.total_shards = peers->total_shards;
-  t.slot_floats = peers->inbox_bytes / sizeof(float) / peers->depth;
+  t.slot_bytes = peers->inbox_bytes / peers->depth;
   return t;
+}
+
+// Checks a finish request against the inbox and turns it into the kernels' form.
+int finish_spec(const b200norm_peers* peers, const b200norm_finish* fin, int* status, FinishSpec* out) {
+  out->out[0] = out->out[1] = nullptr;
+  out->seq = 0; out->status = status; out->slots = 0; out->N = 0; out->w_dtype = B200NORM_F32;
+  if (fin == nullptr) return B200NORM_OK;
+  if ((fin->slots != 1 && fin->slots != 2) || fin->N < 1 || !valid_dtype(fin->w_dtype))
+    return fail(B200NORM_ERR_ARG, "bad finish request (slots=%d N=%lld w_dtype=%d)", fin->slots, (long long)fin->N,
+                fin->w_dtype);
+  if (int rc = check_peers(peers, fin->slots, fin->N, 0)) return rc;
+  out->out[0] = fin->dw;
+  out->out[1] = (fin->slots == 2) ? fin->db : nullptr;
+  out->seq = fin->seq; out->slots = fin->slots; out->N = static_cast<int>(fin->N); out->w_dtype = fin->w_dtype;
+  return B200NORM_OK;
 }
 
 int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, const void* w, const float* mean,
              const float* rstd, void* dx, int64_t dxs, void* dw, void* db, float* group_sums, int row_shards,
              void* workspace, size_t workspace_bytes, int64_t M, int64_t N, int io_dtype, int w_dtype,
              void* stream_v, const b200norm_peers* peers = nullptr, uint64_t seq = 0, int act = 0,
-             const void* bias = nullptr) {
+             const void* bias = nullptr, const b200norm_finish* finish = nullptr) {
   if (int rc = check_common(M, N, io_dtype, w_dtype)) return rc;
   if (!valid_act(act)) return fail(B200NORM_ERR_ARG, "unknown activation code %d", act);
   if (peers != nullptr) {
@@ -400,18 +441,21 @@ int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, con
   }
   if (!want_params) return B200NORM_OK;
 
-  if (peers != nullptr) {  // column reduce fused with the push to every rank's inbox
+  if (peers != nullptr) {  // column reduce fused with the push to every rank's inbox [and a finish]
     ColReducePushParams c;
     c.part[0] = p.dw_part; c.part[1] = p.db_part;
     c.peers = peer_targets(peers);
+    if (int rc = finish_spec(peers, finish, dev->status_dev, &c.fin)) return rc;
     c.seq = seq;
     c.per_shard = plan.ctas_per_shard; c.row_shards = row_shards; c.slots = slots; c.N = static_cast<int>(N);
-    // inbox slots start 16-byte aligned when slot_floats is a multiple of 4
-    if (N % 4 == 0 && c.peers.slot_floats % 4 == 0)
-      return launch(reinterpret_cast<const void*>(&colreduce4_push_kernel),
-                    dim3(static_cast<unsigned>((N + 127) / 128), slots), dim3(32, 16), 0, &c, stream);
-    return launch(reinterpret_cast<const void*>(&colreduce_push_kernel),
-                  dim3(static_cast<unsigned>((N + 31) / 32), slots), dim3(32, 16), 0, &c, stream);
+    // At most 256 CTAs of 512 threads: all resident at once on any device this library runs on, which
+    // the finish phase relies on when it waits for entries other CTAs of the same grid push.
+    const bool wide = N % 4 == 0;
+    const int tiles = static_cast<int>((N + (wide ? 127 : 31)) / (wide ? 128 : 32));
+    const dim3 grid(static_cast<unsigned>(std::min(tiles, 256 / slots)), slots);
+    return launch(wide ? reinterpret_cast<const void*>(&colreduce_push_kernel<4>)
+                       : reinterpret_cast<const void*>(&colreduce_push_kernel<1>),
+                  grid, dim3(32, 16), 0, &c, stream);
   }
 
   ColReduceParams c;
@@ -480,8 +524,7 @@ int softmax_impl(bool bwd, const void* x, int64_t xs, const void* dout, int64_t 
   const bool packets = (N * es) % 16 == 0 && aligned16(x, xs, es) && aligned16(out, os, es) &&
                        (!bwd || aligned16(dout, ds, es));
   const SoftmaxKernel* pk = nullptr;
-  // Tuning aid: B200NORM_FORCE_SOFTMAX = index of the table entry to use when it can hold the row.
-  static const int forced = std::getenv("B200NORM_FORCE_SOFTMAX") ? std::atoi(std::getenv("B200NORM_FORCE_SOFTMAX")) : -1;
+  static const int forced = tuning_env("B200NORM_FORCE_SOFTMAX", -1);
   if (packets && forced >= 0 && forced < k->n && k->kernels[forced].capacity() >= p.V) pk = &k->kernels[forced];
   if (packets)
     for (int i = 0; i < k->n && pk == nullptr; ++i)
@@ -552,8 +595,7 @@ int pnorm_impl(int mode, const void* a, int64_t as, const void* x, int64_t xs, c
   }
   if (packets) {
     const PnormKernel* pk = nullptr;
-    // Tuning aid: B200NORM_FORCE_PNORM = index of the table entry to use when it can hold the row.
-    static const int forced = std::getenv("B200NORM_FORCE_PNORM") ? std::atoi(std::getenv("B200NORM_FORCE_PNORM")) : -1;
+    static const int forced = tuning_env("B200NORM_FORCE_PNORM", -1);
     if (forced >= 0 && forced < k->n && k->kernels[forced].capacity() >= p.V) pk = &k->kernels[forced];
     for (int i = 0; i < k->n && pk == nullptr; ++i)
       if (k->kernels[i].capacity() >= p.V) pk = &k->kernels[i];
@@ -590,8 +632,10 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 static __device__ int g_static_status;  // where this variant's kernels report an expired wait
 
 struct StaticState {
-  DeviceState dev;  // SM count and occupancy cache; no pinned status word is mapped for it
-  void* scratch = nullptr;
+  std::once_flag once;
+  cudaError_t init_err = cudaSuccess;
+  void* scratch = nullptr;     // device address of g_static_scratch
+  int* status_dev = nullptr;   // device address of g_static_status
 };
 StaticState g_static[kMaxDevices];
 
@@ -599,21 +643,22 @@ StaticState g_static[kMaxDevices];
 // device current.  In host code `g_static_scratch` names a host-side stand-in for the device
 // array, not a device address -- handing it to a kernel would fault, or quietly use the wrong
 // memory where the GPU can reach host memory -- so the address is asked for here, once.
-int static_state(StaticState** out) {
+// Launch planning (SM count, occupancies, shared-memory allowances) is the device's one shared
+// record, `dev`: a private copy here once let this path lower an allowance under a launch shape
+// that the other entry points had already cached.
+int static_state(StaticState** out, DeviceState** dev) {
+  if (int rc = device_caches(dev)) return rc;
   int d = -1;
   cudaError_t e = cudaGetDevice(&d);
   if (e != cudaSuccess) return fail(B200NORM_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
-  if (d < 0 || d >= kMaxDevices) return fail(B200NORM_ERR_CUDA, "device index %d out of range", d);
   StaticState& s = g_static[d];
-  std::call_once(s.dev.once, [&]() {
-    s.dev.init_err = cudaDeviceGetAttribute(&s.dev.sm_count, cudaDevAttrMultiProcessorCount, d);
-    if (s.dev.init_err != cudaSuccess) return;
-    s.dev.init_err = cudaGetSymbolAddress(&s.scratch, g_static_scratch);
-    if (s.dev.init_err != cudaSuccess) return;
-    s.dev.init_err = cudaGetSymbolAddress(reinterpret_cast<void**>(&s.dev.status_dev), g_static_status);
+  std::call_once(s.once, [&]() {
+    s.init_err = cudaGetSymbolAddress(&s.scratch, g_static_scratch);
+    if (s.init_err != cudaSuccess) return;
+    s.init_err = cudaGetSymbolAddress(reinterpret_cast<void**>(&s.status_dev), g_static_status);
   });
-  if (s.dev.init_err != cudaSuccess)
-    return fail(B200NORM_ERR_CUDA, "static scratch set-up: %s", cudaGetErrorString(s.dev.init_err));
+  if (s.init_err != cudaSuccess)
+    return fail(B200NORM_ERR_CUDA, "static scratch set-up: %s", cudaGetErrorString(s.init_err));
   *out = &s;
   return B200NORM_OK;
 }
@@ -625,8 +670,9 @@ int rms_bwd_static_impl(const void* x, int64_t xs, const void* dy, int64_t dys, 
   if (M > 0 && (!x || !dy || !dx || !rstd)) return fail(B200NORM_ERR_ARG, "null x / dy / dx / rstd");
   if (xs < N || dys < N || dxs < N) return fail(B200NORM_ERR_ARG, "row stride smaller than N");
   if (M == 0 && dw == nullptr) return B200NORM_OK;
-  StaticState* st;
-  if (int rc = static_state(&st)) return rc;
+  StaticState* st = nullptr;
+  DeviceState* dev = nullptr;
+  if (int rc = static_state(&st, &dev)) return rc;
   const DTypeKernels* k = kernels_for(io_dtype);
   const int es = k->elem_size;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
@@ -634,7 +680,7 @@ int rms_bwd_static_impl(const void* x, int64_t xs, const void* dy, int64_t dys, 
   const bool packets =
       (N * es) % 16 == 0 && aligned16(x, xs, es) && aligned16(dy, dys, es) && aligned16(dx, dxs, es);
   BwdPlan plan;
-  if (int rc = plan_bwd(st->dev, k, kRMS, M, N, packets, &plan)) return rc;
+  if (int rc = plan_bwd(*dev, k, kRMS, M, N, packets, &plan)) return rc;
   const int64_t P = plan.ctas_per_shard;
   if (dw != nullptr && partial_bytes(P, N) > kStaticScratchBytes)
     return fail(B200NORM_ERR_UNSUPPORTED,
@@ -649,7 +695,7 @@ int rms_bwd_static_impl(const void* x, int64_t xs, const void* dy, int64_t dys, 
   p.x_stride = xs; p.dy_stride = dys; p.dx_stride = dxs;
   p.M = M; p.rows_per_shard = M; p.ctas_per_shard = plan.ctas_per_shard;
   p.N = static_cast<int>(N); p.V = static_cast<int>(N * es / 16); p.w_dtype = w_dtype;
-  p.status = st->dev.status_dev;
+  p.status = st->status_dev;
 
   if (plan.pk != nullptr) {
     if (int rc = launch(plan.pk->fn, dim3(static_cast<unsigned>(P * plan.pk->cluster)), dim3(plan.pk->threads()),
@@ -658,8 +704,8 @@ int rms_bwd_static_impl(const void* x, int64_t xs, const void* dy, int64_t dys, 
   } else {
     if (M > 0) {
       int occ;
-      if (int rc = occupancy(st->dev, k->bwd_dx_any[kRMS], 256, 0, &occ)) return rc;
-      const int grid = static_cast<int>(std::min<int64_t>(M, (int64_t)st->dev.sm_count * occ));
+      if (int rc = occupancy(*dev, k->bwd_dx_any[kRMS], 256, 0, &occ)) return rc;
+      const int grid = static_cast<int>(std::min<int64_t>(M, (int64_t)dev->sm_count * occ));
       if (int rc = launch(k->bwd_dx_any[kRMS], dim3(grid), dim3(256), 0, &p, stream, false)) return rc;
     }
     if (dw != nullptr) {
@@ -770,41 +816,36 @@ int b200norm_finalize_dwdb(const float* group_sums, int groups, int slots, void*
 int b200norm_ln_bwd_push(const void* x, int64_t x_row_stride, const void* dy, int64_t dy_row_stride, const void* w,
                          const float* mean, const float* rstd, void* dx, int64_t dx_row_stride, int row_shards,
                          void* workspace, size_t workspace_bytes, int64_t M, int64_t N, int io_dtype, int w_dtype,
-                         const b200norm_peers* peers, uint64_t seq, void* stream) {
+                         const b200norm_peers* peers, uint64_t seq, const b200norm_finish* finish, void* stream) {
   if (peers == nullptr) return fail(B200NORM_ERR_ARG, "null peers");
   return bwd_impl(kLN, x, x_row_stride, dy, dy_row_stride, w, mean, rstd, dx, dx_row_stride, nullptr, nullptr,
-                  nullptr, row_shards, workspace, workspace_bytes, M, N, io_dtype, w_dtype, stream, peers, seq);
+                  nullptr, row_shards, workspace, workspace_bytes, M, N, io_dtype, w_dtype, stream, peers, seq, 0,
+                  nullptr, finish);
 }
 
 int b200norm_rms_bwd_push(const void* x, int64_t x_row_stride, const void* dy, int64_t dy_row_stride, const void* w,
                           const float* rstd, void* dx, int64_t dx_row_stride, int row_shards, void* workspace,
                           size_t workspace_bytes, int64_t M, int64_t N, int io_dtype, int w_dtype,
-                          const b200norm_peers* peers, uint64_t seq, void* stream) {
+                          const b200norm_peers* peers, uint64_t seq, const b200norm_finish* finish, void* stream) {
   if (peers == nullptr) return fail(B200NORM_ERR_ARG, "null peers");
   return bwd_impl(kRMS, x, x_row_stride, dy, dy_row_stride, w, nullptr, rstd, dx, dx_row_stride, nullptr, nullptr,
-                  nullptr, row_shards, workspace, workspace_bytes, M, N, io_dtype, w_dtype, stream, peers, seq);
+                  nullptr, row_shards, workspace, workspace_bytes, M, N, io_dtype, w_dtype, stream, peers, seq, 0,
+                  nullptr, finish);
 }
 
 int b200norm_finalize_pushed(const b200norm_peers* peers, uint64_t seq, int slots, void* dw, void* db, int64_t N,
                              int w_dtype, void* stream) {
-  if (peers == nullptr || (slots != 1 && slots != 2) || N < 1 || !valid_dtype(w_dtype))
-    return fail(B200NORM_ERR_ARG, "bad finalize_pushed arguments (slots=%d N=%lld)", slots, (long long)N);
-  if (int rc = check_peers(peers, slots, N, 0)) return rc;
+  if (peers == nullptr) return fail(B200NORM_ERR_ARG, "null peers");
   DeviceState* dev = nullptr;
   if (int rc = device_state(&dev)) return rc;
+  b200norm_finish fin;
+  fin.seq = seq; fin.slots = slots; fin.w_dtype = w_dtype; fin.N = N; fin.dw = dw; fin.db = db;
   FinalizePushedParams p;
-  p.inbox = static_cast<const float*>(peers->inbox[peers->rank]);
-  p.flags = static_cast<const unsigned long long*>(peers->flags[peers->rank]);
-  p.out[0] = dw;
-  p.out[1] = (slots == 2) ? db : nullptr;
-  p.status = dev->status_dev;
-  p.local = static_cast<LocalState*>(peers->counter);
-  p.seq = seq;
-  p.world = peers->world; p.depth = peers->depth; p.total_shards = peers->total_shards;
-  p.slot_floats = peers->inbox_bytes / sizeof(float) / peers->depth;
-  p.slots = slots; p.N = static_cast<int>(N); p.w_dtype = w_dtype;
+  p.peers = peer_targets(peers);
+  if (int rc = finish_spec(peers, &fin, dev->status_dev, &p.fin)) return rc;
+  const int64_t items = (N % 2 == 0 ? N / 2 : N) * slots;
   return launch(reinterpret_cast<const void*>(&finalize_pushed_kernel),
-                dim3(static_cast<unsigned>((N + 255) / 256), slots), dim3(256), 0, &p,
+                dim3(static_cast<unsigned>(std::min<int64_t>((items + 255) / 256, 256))), dim3(256), 0, &p,
                 static_cast<cudaStream_t>(stream));
 }
 

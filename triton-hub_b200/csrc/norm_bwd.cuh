@@ -117,19 +117,19 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
     bulk_load(dst + row_bytes, gb + r * p.dy_stride + (size_t)v0 * VEC, row_bytes, &bars[s]);
   };
 
-  if (STAGES > 0 && threadIdx.x == 0) {
-    for (int i = 0; i < NBAR; ++i) mbar_init(&full_bar[i], 1);
-    cta_abort = 0;
-    mbar_init_fence();
+  if (STAGES > 0) {
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < NBAR; ++i) mbar_init(&full_bar[i], 1);
+      cta_abort = 0;
+      mbar_init_fence();
+    }
+    __syncthreads();
   }
   grid_dependency_sync();  // nothing above reads global memory
   trigger_dependents();
-  for (int c = threadIdx.x; c < Nl; c += WARPS_M * TPR) {
-    w_s[c] = (p.w != nullptr) ? load_param(p.w, p.w_dtype, (int64_t)v0 * VEC + c) : 1.f;
-    if (ACT != kActNone) b_s[c] = (!RMS && p.b != nullptr) ? load_param(p.b, p.w_dtype, (int64_t)v0 * VEC + c) : 0.f;
-  }
-  __syncthreads();
-  if (CL > 1) cluster_sync_all();  // the partner CTA is running: its shared memory may be written
+  // The first rows are requested before the parameters are read, so that their flight time covers
+  // the parameter set-up (a CTA with a few dozen rows spends a visible share of its life here).
+  // The copies land in this CTA's own shared memory, so a pair's partner need not be running yet.
   if (STAGES > 0 && t == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) {
@@ -137,6 +137,36 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
       if (r < row_end) fill(s, r);
     }
   }
+  // Parameters as fp32 in shared memory: whole packets when they are stored like the rows.
+  const bool w_packets = p.w != nullptr && p.w_dtype == DTypeOf<T>::value && (reinterpret_cast<uintptr_t>(p.w) & 15u) == 0;
+  const bool b_packets = ACT != kActNone && !RMS && p.b != nullptr && p.w_dtype == DTypeOf<T>::value &&
+                         (reinterpret_cast<uintptr_t>(p.b) & 15u) == 0;
+  if (w_packets) {
+    for (int v = threadIdx.x; v < Vl; v += WARPS_M * TPR) {
+      float f[VEC];
+      load_param_packet<T>(p.w, p.w_dtype, v0 + v, f);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) w_s[v * VEC + e] = f[e];
+    }
+  } else {
+    for (int c = threadIdx.x; c < Nl; c += WARPS_M * TPR)
+      w_s[c] = (p.w != nullptr) ? load_param(p.w, p.w_dtype, (int64_t)v0 * VEC + c) : 1.f;
+  }
+  if (ACT != kActNone) {
+    if (b_packets) {
+      for (int v = threadIdx.x; v < Vl; v += WARPS_M * TPR) {
+        float f[VEC];
+        load_param_packet<T>(p.b, p.w_dtype, v0 + v, f);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) b_s[v * VEC + e] = f[e];
+      }
+    } else {
+      for (int c = threadIdx.x; c < Nl; c += WARPS_M * TPR)
+        b_s[c] = (!RMS && p.b != nullptr) ? load_param(p.b, p.w_dtype, (int64_t)v0 * VEC + c) : 0.f;
+    }
+  }
+  __syncthreads();
+  if (CL > 1) cluster_sync_all();  // the partner CTA is running: its shared memory may be written
 
   float dw[LDGS][VEC], db[LDGS][VEC];
 #pragma unroll
@@ -352,12 +382,10 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
     for (int j = 0; j < LDGS; ++j) {
       const int v = j * TPR + t;
       if (v < Vl) {
+        // partial rows start 256-byte aligned and N is a whole number of packets: vector stores
         const size_t o = (size_t)unit * p.N + (size_t)(v0 + v) * VEC;
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-          if (p.dw_part != nullptr) p.dw_part[o + e] = dw[j][e];
-          if (!RMS && p.db_part != nullptr) p.db_part[o + e] = db[j][e];
-        }
+        if (p.dw_part != nullptr) st_f32_vec<VEC>(p.dw_part + o, dw[j]);
+        if (!RMS && p.db_part != nullptr) st_f32_vec<VEC>(p.db_part + o, db[j]);
       }
     }
   }

@@ -185,6 +185,25 @@ __device__ __forceinline__ void st_stream(uint4* p, const uint4& v) {
                : "memory");
 }
 
+// VEC consecutive fp32 values (a thread's share of a dweight / dbias partial row) in one store:
+// a whole 32-byte sector per thread for 8 values, so the memory system sees each sector once
+// instead of once per element.  `p` is aligned to VEC * 4 bytes.
+template <int VEC>
+__device__ __forceinline__ void st_f32_vec(float* p, const float* v) {
+  if constexpr (VEC == 8) {
+    asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "f"(v[0]), "f"(v[1]), "f"(v[2]),
+                 "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7])
+                 : "memory");
+  } else if constexpr (VEC == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  } else if constexpr (VEC == 2) {
+    *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]);
+  } else {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) p[e] = v[e];
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // Programmatic dependent launch.  The kernels are launched with the "programmatic stream
 // serialization" attribute: a kernel may be scheduled while its predecessor in the stream is

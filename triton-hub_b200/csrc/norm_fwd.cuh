@@ -119,13 +119,22 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
       br[j][e] = 0.f;
     }
     if (PREG && v < Vl) {
+      // whole packets when the parameters are stored like the rows and 16-byte aligned
       if (p.w != nullptr) {
+        if ((reinterpret_cast<uintptr_t>(p.w) & 15u) == 0) {
+          load_param_packet<T>(p.w, p.w_dtype, v0 + v, wr[j]);
+        } else {
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) wr[j][e] = load_param(p.w, p.w_dtype, (int64_t)(v0 + v) * VEC + e);
+          for (int e = 0; e < VEC; ++e) wr[j][e] = load_param(p.w, p.w_dtype, (int64_t)(v0 + v) * VEC + e);
+        }
       }
       if (!RMS && p.b != nullptr) {
+        if ((reinterpret_cast<uintptr_t>(p.b) & 15u) == 0) {
+          load_param_packet<T>(p.b, p.w_dtype, v0 + v, br[j]);
+        } else {
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) br[j][e] = load_param(p.b, p.w_dtype, (int64_t)(v0 + v) * VEC + e);
+          for (int e = 0; e < VEC; ++e) br[j][e] = load_param(p.b, p.w_dtype, (int64_t)(v0 + v) * VEC + e);
+        }
       }
     }
   }

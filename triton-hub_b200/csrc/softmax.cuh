@@ -16,13 +16,10 @@
 #include "norm_common.cuh"
 #include "norm_stage.cuh"
 
-// 16-bit Softmax forward: 1 keeps the exponentials of pass 1 in registers and scales them, 0
-// recomputes them from the packed row (fewer registers, one more exponential per element).
-#ifndef B200NORM_SOFTMAX_HOLD16
-#define B200NORM_SOFTMAX_HOLD16 1
-#endif
-
 namespace b200norm {
+
+// Softmax forward keeps the exponentials of pass 1 in registers and scales them (16-bit types too:
+// recomputing them from the packed row saved registers but cost an exponential per element).
 
 struct SoftmaxParams {
   const void* x;     // forward: input; backward: the saved output y
@@ -237,7 +234,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) softmax_kernel(co
 
     // Pass 1: the row reduction.  Forward: per-thread maximum m_t and s = sum exp(x - m_t), merged
     // over the group; backward: sum(dout) or sum(dout * y).
-    constexpr bool HOLD = !BWD && !LOG && (sizeof(T) >= 4 || B200NORM_SOFTMAX_HOLD16);
+    constexpr bool HOLD = !BWD && !LOG;
     float held[HOLD ? LDGS : 1][VEC];  // Softmax forward: the exponentials, scaled in pass 2
     float m_t = 0.f, m_row = 0.f, s_row = 0.f;
     if (!BWD) {
