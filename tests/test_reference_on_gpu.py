@@ -1,0 +1,92 @@
+"""This library against the UNMODIFIED reference running on the same GPU.
+
+When the reference is installed under baseline/_ref (the build step installs it where its source
+tree is at hand), baseline/run_reference_ops_gpu.py runs its own modules -- LayerNorm, RMSNorm,
+GeLU, Softmax / LogSoftmax / Softmin, Ops.norm / Ops.normalize with p in {1, 2, 2.5, 3} -- in a child
+process on seeded inputs and saves y, dx, dweight, dbias; the same inputs then go through this
+library's drop-in modules and the results are compared at the usual bars (1e-5 of the tensor's
+largest magnitude for fp32, 1e-2 for 16-bit types).  This is the only place where the reference's
+general-p branch (libdevice pow, which Triton's interpreter cannot run) is compared directly.
+
+The child process keeps the reference's `TritonHub` package and this repository's drop-in of the
+same name apart.  Skipped where baseline/_ref is absent.
+"""
+import importlib.util
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from helpers import TOL, assert_parity
+
+ROOT = Path(__file__).resolve().parent.parent
+RUNNER = ROOT / "baseline" / "run_reference_ops_gpu.py"
+DEV = "cuda:0"
+
+_spec = importlib.util.spec_from_file_location("run_reference_ops_gpu", RUNNER)
+_runner = importlib.util.module_from_spec(_spec)
+_spec.loader.exec_module(_runner)
+CASES = _runner.CASES
+
+
+@pytest.fixture(scope="module")
+def reference_outputs(tmp_path_factory):
+    if not (ROOT / "baseline" / "_ref" / "TritonHub").is_dir():
+        pytest.skip("the reference is not installed under baseline/_ref")
+    out = tmp_path_factory.mktemp("ref") / "reference_outputs.npz"
+    res = subprocess.run([sys.executable, str(RUNNER), str(out)], capture_output=True, text=True, timeout=900)
+    if res.returncode != 0:
+        pytest.skip("the reference did not run here: " + (res.stderr.strip().splitlines() or ["no output"])[-1][:200])
+    z = np.load(out)
+    if "unavailable" in z.files:
+        pytest.skip(str(z["unavailable"]))
+    return z
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
+def test_same_inputs_through_the_reference_and_through_this_library(case, reference_outputs):
+    from TritonHub.Activations import GeLU, LogSoftmax, Softmax, Softmin      # this repository's drop-ins
+    from TritonHub.Normalization import LayerNorm, RMSNorm
+    from TritonHub.Ops import norm, normalize
+    import TritonHub
+    assert "baseline" not in str(Path(TritonHub.__file__).resolve()), "the drop-in package, not the reference"
+
+    name, kind, dtype, shape, extra = case
+    x, dy, w, b = _runner.make_inputs(name, dtype, shape)
+    x = x.to(DEV).requires_grad_(True)
+    dy = dy.to(DEV)
+    got = {}
+    if kind in ("ln", "rms"):
+        N = shape[-1]
+        mod = (LayerNorm(N, eps=extra, elementwise_affine=True, bias=True, device=DEV, dtype=x.dtype) if kind == "ln"
+               else RMSNorm(N, eps=extra, elementwise_affine=True, device=DEV, dtype=x.dtype))
+        with torch.no_grad():
+            mod.weight.copy_(w.to(DEV))
+            if kind == "ln":
+                mod.bias.copy_(b.to(DEV))
+        y = mod(x)
+        y.backward(dy)
+        got = {"y": y, "dx": x.grad, "dw": mod.weight.grad}
+        if kind == "ln":
+            got["db"] = mod.bias.grad
+    else:
+        if kind == "gelu":
+            y = GeLU(approximate=extra)(x)
+        elif kind in ("softmax", "logsoftmax", "softmin"):
+            y = {"softmax": Softmax, "logsoftmax": LogSoftmax, "softmin": Softmin}[kind]()(x)
+        elif kind == "norm":
+            y = norm(p=extra, eps=1e-6)(x)
+        else:
+            y = normalize(p=extra, eps=1e-6)(x)
+        y.backward(dy[..., 0].contiguous() if kind == "norm" else dy)
+        got = {"y": y, "dx": x.grad}
+    torch.cuda.synchronize()
+    tol = TOL[dtype]
+    for key, t in got.items():
+        ref = reference_outputs[f"{name}/{key}"]
+        assert_parity(t.detach().float().cpu().numpy(), ref, tol, f"{name} {key} vs the reference on this GPU")

@@ -47,13 +47,12 @@ def _headers_mtime() -> float:
     return max(h.stat().st_mtime for h in headers)
 
 
-def _compile(src: Path, verbose: bool, ptxas_info: bool) -> Path:
+def _compile(src: Path, verbose: bool, ptxas_info: bool, defines: tuple = ()) -> Path:
     obj = BUILD_DIR / (src.stem + ".o")
     newest = max(src.stat().st_mtime, _headers_mtime())
     if obj.exists() and obj.stat().st_mtime >= newest:
         return obj
-    extra = os.environ.get("B200NORM_NVCC_EXTRA", "").split()  # e.g. -DB200NORM_SOFTMAX_CANDIDATES (tuning builds)
-    cmd = [_nvcc(), *NVCC_FLAGS, *extra, f"-I{INCLUDE}", f"-I{CSRC}", "-c", str(src), "-o", str(obj)]
+    cmd = [_nvcc(), *NVCC_FLAGS, *(f"-D{d}" for d in defines), f"-I{INCLUDE}", f"-I{CSRC}", "-c", str(src), "-o", str(obj)]
     if ptxas_info:
         cmd[1:1] = ["-Xptxas", "-v"]
     if verbose:
@@ -70,15 +69,18 @@ def _compile(src: Path, verbose: bool, ptxas_info: bool) -> Path:
     return obj
 
 
-def build_library(verbose: bool = False, force: bool = False, ptxas_info: bool = False) -> Path:
-    """Compile every ``csrc/*.cu`` for sm_100a and link ``libb200norm.so``; returns its path."""
+def build_library(verbose: bool = False, force: bool = False, ptxas_info: bool = False, defines: tuple = ()) -> Path:
+    """Compile every ``csrc/*.cu`` for sm_100a and link ``libb200norm.so``; returns its path.
+    ``defines``: preprocessor symbols for a non-default build (``--define NAME`` on the command line), e.g.
+    B200NORM_TUNING, which compiles in the environment-variable overrides of the launch table; such a
+    build must be forced (``--force``), and forced again to return to the shipped configuration."""
     BUILD_DIR.mkdir(parents=True, exist_ok=True)
     if force:
         for o in BUILD_DIR.glob("*.o"):
             o.unlink()
     srcs = _sources()
     with ThreadPoolExecutor(max_workers=min(len(srcs), max(2, (os.cpu_count() or 4) - 2))) as pool:
-        objs = list(pool.map(lambda s: _compile(s, verbose, ptxas_info), srcs))
+        objs = list(pool.map(lambda s: _compile(s, verbose, ptxas_info, tuple(defines)), srcs))
     if LIB_PATH.exists() and all(LIB_PATH.stat().st_mtime >= o.stat().st_mtime for o in objs):
         return LIB_PATH
     cmd = [_nvcc(), "-shared", "-o", str(LIB_PATH), *map(str, objs),
@@ -92,5 +94,6 @@ def build_library(verbose: bool = False, force: bool = False, ptxas_info: bool =
 
 
 if __name__ == "__main__":
-    path = build_library(verbose=True, force="--force" in sys.argv, ptxas_info="--ptxas" in sys.argv)
+    defs = tuple(sys.argv[i + 1] for i, a in enumerate(sys.argv[:-1]) if a == "--define")
+    path = build_library(verbose=True, force="--force" in sys.argv, ptxas_info="--ptxas" in sys.argv, defines=defs)
     print(path)
