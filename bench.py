@@ -190,12 +190,12 @@ class Measurement:
         self.approx = {"gelu": "none", "gelu_tanh": "tanh"}.get(act)
         self.unfused = unfused
         self.exchange = None
-        if world > 1:
+        if world > 1 or args.push_on_one_gpu:
             from b200norm.parallel import GradExchange, PushExchange
             self.exchange = (PushExchange(max_n=self.N, slots=2, device=device,
                                           total_shards=8 if g_invariant else None, device_numbering=args.graph)
                              if args.exchange == "push" else GradExchange(mode=args.exchange))
-        self.push = world > 1 and args.exchange == "push"
+        self.push = self.exchange is not None and args.exchange == "push"
 
     # -- pieces of a step ------------------------------------------------------------------------
     def forward(self):
@@ -242,7 +242,7 @@ class Measurement:
                 return (Fn._layernorm_bwd(x, dyy, w, b, mean, rstd, eps) if self.ln
                         else Fn._rmsnorm_bwd(x, dyy, w, rstd, eps)), None
             return Act._norm_gelu_bwd("ln" if self.ln else "rms", x, dy, w, b, mean, rstd, eps, self.approx), None
-        if self.world == 1:
+        if self.exchange is None:
             return (Fn._layernorm_bwd(x, dy, w, b, mean, rstd, eps) if self.ln
                     else Fn._rmsnorm_bwd(x, dy, w, rstd, eps)), None
         ex = self.exchange
@@ -280,7 +280,7 @@ class Measurement:
         stream; blocks repeat until the timed region lasts `min_seconds` (so that clock samples fall
         inside it) and the MEDIAN block is reported.  All ranks start together (barrier + synchronize)
         and the block times are the max over ranks."""
-        graph_mode = self.args.graph and (self.world == 1 or self.push)
+        graph_mode = self.args.graph and (self.exchange is None or self.push)
         pend = None
         for _ in range(max(warmup, 3)):
             saved = self.forward()
@@ -513,7 +513,7 @@ def run_gpu(args):
     K = args.steps
     m = Measurement(args.workload, wl, args.scaling, args, device, world, rank, act=args.act, unfused=args.unfused,
                     g_invariant=args.g_invariant)
-    res = m.run(K, args.warmup, sampler)
+    res = m.run(K, args.warmup, sampler, min_seconds=args.min_seconds)
     sampler.stop_flag = True
     sampler.join(timeout=1.0)
     clocks = sampler.summary()
@@ -969,6 +969,11 @@ def main():
                     help="with --workload custom: the norms, or one of the ops built around them (single GPU, p = 2)")
     ap.add_argument("--dtype", choices=sorted(TDTYPE), help="with --workload custom: storage type")
     ap.add_argument("--dim", type=int, default=0, help="with --workload custom: row length")
+    ap.add_argument("--min-seconds", type=float, default=0.25,
+                    help="repeat the block of --steps steps until the timed region lasts this long (0: one block)")
+    ap.add_argument("--push-on-one-gpu", action="store_true",
+                    help="one GPU: run the multi-GPU step (push exchange with world = 1, the pushes land in this "
+                         "GPU's own inbox) -- for profiling its kernels, which a profiler can only watch on one GPU")
     ap.add_argument("--no-also", action="store_true",
                     help="several GPUs: skip the c4 / c5 strong-scaling measurements reported under `also`")
     ap.add_argument("--no-module", action="store_true", help="skip timing the public module path (module_eager_ms_per_step)")

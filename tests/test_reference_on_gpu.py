@@ -6,7 +6,10 @@ GeLU, Softmax / LogSoftmax / Softmin, Ops.norm / Ops.normalize with p in {1, 2, 
 process on seeded inputs and saves y, dx, dweight, dbias; the same inputs then go through this
 library's drop-in modules and the results are compared at the usual bars (1e-5 of the tensor's
 largest magnitude for fp32, 1e-2 for 16-bit types).  This is the only place where the reference's
-general-p branch (libdevice pow, which Triton's interpreter cannot run) is compared directly.
+general-p branch (libdevice pow, which Triton's interpreter cannot run) is compared directly: the
+norm's forward and backward and normalize's forward.  normalize's BACKWARD for p other than 1 and 2
+cannot run in the reference at all (its kernel calls `pow` without importing it and raises
+NameError); the runner records that and the test says so instead of comparing.
 
 The child process keeps the reference's `TritonHub` package and this repository's drop-in of the
 same name apart.  Skipped where baseline/_ref is absent.
@@ -87,6 +90,16 @@ def test_same_inputs_through_the_reference_and_through_this_library(case, refere
         got = {"y": y, "dx": x.grad}
     torch.cuda.synchronize()
     tol = TOL[dtype]
+    compared = 0
     for key, t in got.items():
+        if f"{name}/{key}" not in reference_outputs.files:
+            continue                # the reference failed before producing this tensor (see below)
         ref = reference_outputs[f"{name}/{key}"]
         assert_parity(t.detach().float().cpu().numpy(), ref, tol, f"{name} {key} vs the reference on this GPU")
+        compared += 1
+    if f"{name}/error" in reference_outputs.files:
+        # e.g. Ops.normalize's backward for p other than 1 and 2: TritonHub/Ops/normalize.py:83,115 call `pow`
+        # without importing it (Ops/norm.py:4 does), so the reference raises NameError there.
+        pytest.skip(f"the reference itself fails on this case after {compared} tensor(s) compared: "
+                    f"{reference_outputs[name + '/error']}")
+    assert compared == len(got)

@@ -16,6 +16,7 @@
 #include "norm_colreduce.cuh"
 #include "norm_fwd.cuh"
 #include "norm_push.cuh"
+#include "norm_rows_any.cuh"
 #include "norm_table.h"
 #include "pnorm.cuh"
 #include "softmax.cuh"
@@ -172,7 +173,13 @@ bool aligned16(const void* p, int64_t stride_elems, int es) {
   return (reinterpret_cast<uintptr_t>(p) & 15u) == 0 && ((stride_elems * es) & 15) == 0;
 }
 
-// First table entry whose capacity covers a row of V packets, or null.
+// Shape of the any-alignment row kernels for a row of N elements (norm_table.h).
+int row_shape(int64_t N) {
+  for (int i = 0; i < 4; ++i)
+    if ((int64_t)kRowShapes[i].threads * kRowShapes[i].columns >= N) return i;
+  return 3;  // unreachable: 1024 x 32 covers the 64 KB row limit for every storage type
+}
+
 // Dynamic shared memory of a backward launch, per CTA: (warps_m [+1 with a fused activation: the
 // bias]) x columns fp32 for the weights and the row-group sums, padded to 128 bytes, then the
 // x + dy row slots.  A CTA of a pair holds half of the columns.
@@ -235,6 +242,29 @@ int launch(const void* fn, dim3 grid, dim3 block, size_t smem, void* params, cud
   return B200NORM_OK;
 }
 
+// Launches an any-alignment row kernel (forward: one staged row per ring slot, backward dx: two).
+// Shared memory per CTA = (rows_per_slot * slots + 1) row buffers; four slots when that leaves room
+// for a second CTA on the SM, else as many as fit.
+int launch_row_kernel(DeviceState& dev, const void* const (&fns)[4], int64_t M, int64_t N, int es, int rows_per_slot,
+                      void* params, cudaStream_t stream) {
+  const int shape = row_shape(N);
+  const void* fn = fns[shape];
+  const int threads = kRowShapes[shape].threads;
+  const size_t buf = row_buffer_bytes(N, es);
+  auto bytes = [&](int slots) { return (static_cast<size_t>(rows_per_slot) * slots + 1) * buf; };
+  int slots = 4;
+  while (slots > 2 && bytes(slots) > 112 * 1024) --slots;
+  if (bytes(slots) > 112 * 1024) {  // wide rows: one CTA per SM, as many slots as its shared memory holds
+    slots = 4;
+    while (slots > 1 && bytes(slots) > kMaxSmemPerCta - 4096) --slots;
+  }
+  const size_t smem = bytes(slots);
+  int occ;
+  if (int rc = occupancy(dev, fn, threads, smem, &occ)) return rc;
+  const int grid = static_cast<int>(std::min<int64_t>(M, (int64_t)dev.sm_count * occ));
+  return launch(fn, dim3(grid), dim3(threads), smem, params, stream, false);
+}
+
 int check_common(int64_t M, int64_t N, int io_dtype, int w_dtype) {
   if (!valid_dtype(io_dtype) || !valid_dtype(w_dtype))
     return fail(B200NORM_ERR_ARG, "unknown dtype code (io %d, w %d)", io_dtype, w_dtype);
@@ -284,10 +314,7 @@ int fwd_impl(int op, const void* x, int64_t xs, const void* w, const void* b, vo
     return fail(B200NORM_ERR_UNSUPPORTED,
                 "a fused activation needs rows whose base, stride and length are multiples of 16 bytes; run the norm "
                 "and b200norm_gelu_fwd separately");
-  int occ;
-  if (int rc = occupancy(*dev, k->fwd_any[op], 256, 0, &occ)) return rc;
-  const int grid = static_cast<int>(std::min<int64_t>(M, (int64_t)dev->sm_count * occ));
-  return launch(k->fwd_any[op], dim3(grid), dim3(256), 0, &p, static_cast<cudaStream_t>(stream), false);
+  return launch_row_kernel(*dev, k->fwd_rows[op], M, N, es, 1, &p, static_cast<cudaStream_t>(stream));
 }
 
 // How a backward call is laid out: which kernel, how many partial rows.
@@ -429,10 +456,7 @@ int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, con
       return rc;
   } else {
     if (M > 0) {
-      int occ;
-      if (int rc = occupancy(*dev, k->bwd_dx_any[op], 256, 0, &occ)) return rc;
-      const int grid = static_cast<int>(std::min<int64_t>(M, (int64_t)dev->sm_count * occ));
-      if (int rc = launch(k->bwd_dx_any[op], dim3(grid), dim3(256), 0, &p, stream, false)) return rc;
+      if (int rc = launch_row_kernel(*dev, k->bwd_dx_rows[op], M, N, es, 2, &p, stream)) return rc;
     }
     if (want_params) {
       const dim3 grid(static_cast<unsigned>((N + 255) / 256), static_cast<unsigned>(P));
@@ -703,10 +727,7 @@ int rms_bwd_static_impl(const void* x, int64_t xs, const void* dy, int64_t dys, 
       return rc;
   } else {
     if (M > 0) {
-      int occ;
-      if (int rc = occupancy(*dev, k->bwd_dx_any[kRMS], 256, 0, &occ)) return rc;
-      const int grid = static_cast<int>(std::min<int64_t>(M, (int64_t)dev->sm_count * occ));
-      if (int rc = launch(k->bwd_dx_any[kRMS], dim3(grid), dim3(256), 0, &p, stream, false)) return rc;
+      if (int rc = launch_row_kernel(*dev, k->bwd_dx_rows[kRMS], M, N, es, 2, &p, stream)) return rc;
     }
     if (dw != nullptr) {
       const dim3 grid(static_cast<unsigned>((N + 255) / 256), static_cast<unsigned>(P));

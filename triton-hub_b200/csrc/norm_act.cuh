@@ -70,6 +70,79 @@ __device__ __forceinline__ float act_grad(float x) {
   return 1.f;
 }
 
+// ---------------------------------------------------------------------------------------
+// The same, two elements per instruction (packed fp32 arithmetic, norm_common.cuh): every
+// multiply-add of the formulas above is done on pairs; only the special-function calls (ex2, rcp)
+// and the sign / select steps stay scalar.  Bit for bit the results of act_fwd / act_grad.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float2 gelu_tanh_r2(float2 x, float2 x2) {
+  const float2 arg = mul2(x, fma2(x2, splat2(kGeluK * 0.044715f * 2.f * kLog2e), splat2(kGeluK * 2.f * kLog2e)));
+  const float2 d = add2(make_float2(ex2_fast(arg.x), ex2_fast(arg.y)), splat2(1.f));
+  return make_float2(rcp_fast(d.x), rcp_fast(d.y));
+}
+
+__device__ __forceinline__ float2 gelu_erf_q2(float2 x, float2& e) {
+  const float2 arg = mul2(mul2(x, x), splat2(-0.5f * kLog2e));
+  e = make_float2(ex2_fast(arg.x), ex2_fast(arg.y));
+  const float2 d = fma2(splat2(0.3275911f * 0.70710678118654752f), make_float2(fabsf(x.x), fabsf(x.y)), splat2(1.f));
+  const float2 t = make_float2(rcp_fast(d.x), rcp_fast(d.y));
+  float2 poly = fma2(t, splat2(0.5307027145f), splat2(-0.7265760135f));
+  poly = fma2(t, poly, splat2(0.7107068705f));
+  poly = fma2(t, poly, splat2(-0.142248368f));
+  poly = fma2(t, poly, splat2(0.127414796f));
+  return mul2(mul2(t, poly), e);
+}
+
+template <int ACT>
+__device__ __forceinline__ float2 act_fwd2(float2 x) {
+  if (ACT == kActGeluErf) {
+    float2 e;
+    const float2 q = gelu_erf_q2(x, e);
+    return fma2(make_float2(-fabsf(x.x), -fabsf(x.y)), q, make_float2(fmaxf(x.x, 0.f), fmaxf(x.y, 0.f)));
+  } else if (ACT == kActGeluTanh) {
+    return fma2(mul2(x, splat2(-1.f)), gelu_tanh_r2(x, mul2(x, x)), x);
+  }
+  return x;
+}
+
+template <int ACT>
+__device__ __forceinline__ float2 act_grad2(float2 x) {
+  if (ACT == kActGeluErf) {
+    float2 e;
+    const float2 q = gelu_erf_q2(x, e);
+    const float2 up = fma2(q, splat2(-1.f), splat2(1.f));  // 1 - q
+    const float2 cdf = make_float2(x.x >= 0.f ? up.x : q.x, x.y >= 0.f ? up.y : q.y);
+    return fma2(x, mul2(e, splat2(0.39894228040143268f)), cdf);  // Phi + x * phi
+  } else if (ACT == kActGeluTanh) {
+    const float2 x2 = mul2(x, x);
+    const float2 r = gelu_tanh_r2(x, x2);
+    const float2 s = fma2(r, splat2(-1.f), splat2(1.f));  // 1 - r
+    const float2 xup2 = mul2(x, fma2(x2, splat2(2.f * 3.f * 0.044715f * kGeluK), splat2(2.f * kGeluK)));  // 2 x u'
+    return fma2(xup2, mul2(r, s), s);
+  }
+  return splat2(1.f);
+}
+
+// y <- act(y) and g <- g * act'(y) over a packet's VEC values (VEC is even for every storage type).
+template <int ACT, int VEC>
+__device__ __forceinline__ void act_fwd_packet(float (&y)[VEC]) {
+#pragma unroll
+  for (int e = 0; e < VEC; e += 2) {
+    const float2 r = act_fwd2<ACT>(make_float2(y[e], y[e + 1]));
+    y[e] = r.x;
+    y[e + 1] = r.y;
+  }
+}
+template <int ACT, int VEC>
+__device__ __forceinline__ void act_grad_mul_packet(const float (&y)[VEC], float (&g)[VEC]) {
+#pragma unroll
+  for (int e = 0; e < VEC; e += 2) {
+    const float2 r = mul2(make_float2(g[e], g[e + 1]), act_grad2<ACT>(make_float2(y[e], y[e + 1])));
+    g[e] = r.x;
+    g[e + 1] = r.y;
+  }
+}
+
 // Stand-alone element-wise GeLU (gelu.py:12-29, 56-81): y = gelu(x), or dx = dout * gelu'(x).
 struct ActParams {
   const void* x;
@@ -96,11 +169,13 @@ __global__ void __launch_bounds__(256) act_kernel(const ActParams p) {
       float gf[VEC];
       Pack16<T>::unpack(
           ld_stream(reinterpret_cast<const uint4*>(static_cast<const T*>(p.dout) + row * p.dout_stride) + v), gf);
+      act_grad_mul_packet<ACT, VEC>(xf, gf);
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) o[e] = gf[e] * act_grad<ACT>(xf[e]);
+      for (int e = 0; e < VEC; ++e) o[e] = gf[e];
     } else {
+      act_fwd_packet<ACT, VEC>(xf);
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) o[e] = act_fwd<ACT>(xf[e]);
+      for (int e = 0; e < VEC; ++e) o[e] = xf[e];
     }
     st_stream(reinterpret_cast<uint4*>(static_cast<T*>(p.out) + row * p.out_stride) + v, Pack16<T>::pack(o));
   }

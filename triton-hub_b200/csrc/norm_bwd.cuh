@@ -127,52 +127,42 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
   }
   grid_dependency_sync();  // nothing above reads global memory
   trigger_dependents();
-  // The first rows are requested before the parameters are read, so that their flight time covers
-  // the parameter set-up (a CTA with a few dozen rows spends a visible share of its life here).
-  // The copies land in this CTA's own shared memory, so a pair's partner need not be running yet.
-  if (STAGES > 0 && t == 0) {
+  // The first rows are requested right behind the (small) parameter loads and land while the
+  // parameters are staged (a CTA with a few dozen rows spends a visible share of its life here).
+  // The copies go to this CTA's own shared memory, so a pair's partner need not be running yet.
+  auto first_fills = [&]() {
+    if (STAGES > 0 && t == 0) {
 #pragma unroll
-    for (int s = 0; s < STAGES; ++s) {
-      const int64_t r = first + s * step;
-      if (r < row_end) fill(s, r);
-    }
-  }
-  // Parameters as fp32 in shared memory: whole packets when they are stored like the rows.
-  const bool w_packets = p.w != nullptr && p.w_dtype == DTypeOf<T>::value && (reinterpret_cast<uintptr_t>(p.w) & 15u) == 0;
-  const bool b_packets = ACT != kActNone && !RMS && p.b != nullptr && p.w_dtype == DTypeOf<T>::value &&
-                         (reinterpret_cast<uintptr_t>(p.b) & 15u) == 0;
-  if (w_packets) {
-    for (int v = threadIdx.x; v < Vl; v += WARPS_M * TPR) {
-      float f[VEC];
-      load_param_packet<T>(p.w, p.w_dtype, v0 + v, f);
-#pragma unroll
-      for (int e = 0; e < VEC; ++e) w_s[v * VEC + e] = f[e];
-    }
-  } else {
-    for (int c = threadIdx.x; c < Nl; c += WARPS_M * TPR)
-      w_s[c] = (p.w != nullptr) ? load_param(p.w, p.w_dtype, (int64_t)v0 * VEC + c) : 1.f;
-  }
-  if (ACT != kActNone) {
-    if (b_packets) {
-      for (int v = threadIdx.x; v < Vl; v += WARPS_M * TPR) {
-        float f[VEC];
-        load_param_packet<T>(p.b, p.w_dtype, v0 + v, f);
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) b_s[v * VEC + e] = f[e];
+      for (int s = 0; s < STAGES; ++s) {
+        const int64_t r = first + s * step;
+        if (r < row_end) fill(s, r);
       }
-    } else {
-      for (int c = threadIdx.x; c < Nl; c += WARPS_M * TPR)
-        b_s[c] = (!RMS && p.b != nullptr) ? load_param(p.b, p.w_dtype, (int64_t)v0 * VEC + c) : 0.f;
     }
-  }
+  };
+  // Parameters as fp32 in shared memory.  Thread t of row group m fetches the packets j * TPR + t with
+  // j % WARPS_M == m: between them the groups cover every column once.
+  if (p.w == nullptr)
+    for (int c = threadIdx.x; c < Nl; c += WARPS_M * TPR) w_s[c] = 1.f;
+  if (ACT != kActNone && (RMS || p.b == nullptr))
+    for (int c = threadIdx.x; c < Nl; c += WARPS_M * TPR) b_s[c] = 0.f;
+  load_param_packets<T, LDGS>(
+      p.w, (ACT != kActNone && !RMS) ? p.b : nullptr, p.w_dtype, v0, t, TPR, Vl,
+      [&](int j) { return WARPS_M == 1 || (j % WARPS_M) == warp_m; }, first_fills,
+      [&](int which, int j, const float* f) {
+        float* dst = (which == 0 ? w_s : b_s) + (j * TPR + t) * VEC;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) dst[e] = f[e];
+      });
   __syncthreads();
   if (CL > 1) cluster_sync_all();  // the partner CTA is running: its shared memory may be written
 
-  float dw[LDGS][VEC], db[LDGS][VEC];
+  // Per-element values live as fp32 pairs (two per instruction, norm_common.cuh): H pairs per packet.
+  constexpr int H = VEC / 2;
+  float2 dw[LDGS][H], db[LDGS][H];
 #pragma unroll
   for (int j = 0; j < LDGS; ++j)
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) dw[j][e] = db[j][e] = 0.f;
+    for (int h = 0; h < H; ++h) dw[j][h] = db[j][h] = splat2(0.f);
 
   uint4 xv[LDGS], gv[LDGS];
   auto fetch = [&](int64_t r, uint4* xo, uint4* go) {  // STAGES == 0: straight from global
@@ -226,48 +216,53 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
       }
     }
 
-    // Pass 1: dweight / dbias sums and the two row sums (layernorm.py:132-138).
-    float s[NV];
-#pragma unroll
-    for (int i = 0; i < NV; ++i) s[i] = 0.f;
+    // Pass 1: dweight / dbias sums and the two row sums (layernorm.py:132-138).  The row sums run as
+    // two chains (the lanes of a pair), added at the end.
+    float2 s0 = splat2(0.f), s1 = splat2(0.f);
     constexpr int KL = KEEP ? LDGS : 1;
-    float xh_k[KL][VEC], wdy_k[KL][VEC];
+    float2 xh_k[KL][H], wdy_k[KL][H];
+    const float2 nmu2 = splat2(-mu), rs2 = splat2(rs);
 #pragma unroll
     for (int j = 0; j < LDGS; ++j) {
       const int v = j * TPR + t;
       if (v < Vl) {
-        float xf[VEC], gf[VEC];
-        Pack16<T>::unpack(xv[j], xf);
-        Pack16<T>::unpack(gv[j], gf);
+        float2 xf[H], gf[H];
+        Pack16<T>::unpack2(xv[j], xf);
+        Pack16<T>::unpack2(gv[j], gf);
+        const float2* w2 = reinterpret_cast<const float2*>(&w_s[v * VEC]);
         if (ACT != kActNone) {
           // dy = dz * act'(y) with y = xhat*w + b rebuilt from the row.  When pass 2 reads the packed
           // row again, dy replaces dz there, rounded to the storage type as a separate activation
           // backward would have stored it; the kept form carries it on in fp32.
+          const float2* b2 = reinterpret_cast<const float2*>(&b_s[v * VEC]);
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) {
-            const float y = fmaf((xf[e] - mu) * rs, w_s[v * VEC + e], b_s[v * VEC + e]);
-            gf[e] *= act_grad<ACT>(y);
+          for (int h = 0; h < H; ++h) {
+            const float2 y = fma2(mul2(add2(xf[h], nmu2), rs2), w2[h], b2[h]);
+            gf[h] = mul2(gf[h], act_grad2<ACT>(y));
           }
           if (!KEEP) {
-            gv[j] = Pack16<T>::pack(gf);
-            Pack16<T>::unpack(gv[j], gf);
+            gv[j] = Pack16<T>::pack2(gf);
+            Pack16<T>::unpack2(gv[j], gf);
           }
         }
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-          const float xh = (xf[e] - mu) * rs;
-          const float wdy = w_s[v * VEC + e] * gf[e];
-          dw[j][e] += gf[e] * xh;
-          if (!RMS) db[j][e] += gf[e];
-          s[0] += xh * wdy;
-          if (!RMS) s[NV - 1] += wdy;
+        for (int h = 0; h < H; ++h) {
+          const float2 xh = mul2(add2(xf[h], nmu2), rs2);
+          const float2 wdy = mul2(w2[h], gf[h]);
+          dw[j][h] = fma2(gf[h], xh, dw[j][h]);
+          if (!RMS) db[j][h] = add2(db[j][h], gf[h]);
+          s0 = fma2(xh, wdy, s0);
+          if (!RMS) s1 = add2(s1, wdy);
           if (KEEP) {
-            xh_k[j][e] = xh;
-            wdy_k[j][e] = wdy;
+            xh_k[j][h] = xh;
+            wdy_k[j][h] = wdy;
           }
         }
       }
     }
+    float s[NV];
+    s[0] = s0.x + s0.y;
+    if (!RMS) s[NV - 1] = s1.x + s1.y;
     // With a single row group its barrier is the CTA's barrier 0; several groups keep 1, 2, ... because
     // a group that has finished its rows waits on barrier 0 (the final sum) while the others still loop.
     group_sum<WARPS_N, NV, (WARPS_M == 1 ? 0 : 1)>(s, red_smem[warp_m], phase, warp_m, warp_n, lane);
@@ -306,22 +301,24 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
     uint4* dxrow = reinterpret_cast<uint4*>(dxb + row * p.dx_stride) + v0;
     const float k1 = -c1 * rs, k2 = -c2 * rs;
     const float kb = k1 * rs, kc = -kb * mu + k2;
+    const float2 k1_2 = splat2(k1), k2_2 = splat2(k2), kb2 = splat2(kb), kc2 = splat2(kc);
 #pragma unroll
     for (int j = 0; j < LDGS; ++j) {
       const int v = j * TPR + t;
       if (v < Vl) {
-        float o[VEC];
+        float2 o[H];
         if (KEEP) {
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) o[e] = fmaf(xh_k[j][e], k1, fmaf(wdy_k[j][e], rs, k2));
+          for (int h = 0; h < H; ++h) o[h] = fma2(xh_k[j][h], k1_2, fma2(wdy_k[j][h], rs2, k2_2));
         } else {
-          float xf[VEC], gf[VEC];
-          Pack16<T>::unpack(xv[j], xf);
-          Pack16<T>::unpack(gv[j], gf);
+          float2 xf[H], gf[H];
+          Pack16<T>::unpack2(xv[j], xf);
+          Pack16<T>::unpack2(gv[j], gf);
+          const float2* w2 = reinterpret_cast<const float2*>(&w_s[v * VEC]);
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) o[e] = fmaf(w_s[v * VEC + e] * rs, gf[e], fmaf(xf[e], kb, kc));
+          for (int h = 0; h < H; ++h) o[h] = fma2(mul2(w2[h], rs2), gf[h], fma2(xf[h], kb2, kc2));
         }
-        st_stream(dxrow + v, Pack16<T>::pack(o));
+        st_stream(dxrow + v, Pack16<T>::pack2(o));
       }
     }
 
@@ -354,9 +351,9 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
       for (int j = 0; j < LDGS; ++j) {
         const int v = j * TPR + t;
         if (v < Vl) {
+          float2* dst = reinterpret_cast<float2*>(&acc[(size_t)warp_m * Nl + v * VEC]);
 #pragma unroll
-          for (int e = 0; e < VEC; ++e)
-            acc[(size_t)warp_m * Nl + v * VEC + e] = (pass == 0) ? dw[j][e] : db[j][e];
+          for (int h = 0; h < H; ++h) dst[h] = (pass == 0) ? dw[j][h] : db[j][h];
         }
       }
       __syncthreads();
@@ -366,11 +363,12 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
           const int v = j * TPR + t;
           if (v < Vl) {
 #pragma unroll
-            for (int e = 0; e < VEC; ++e) {
-              float a = 0.f;
-              for (int m = 0; m < WARPS_M; ++m) a += acc[(size_t)m * Nl + v * VEC + e];
-              if (pass == 0) dw[j][e] = a;
-              else db[j][e] = a;
+            for (int h = 0; h < H; ++h) {
+              float2 a = splat2(0.f);
+              for (int m = 0; m < WARPS_M; ++m)
+                a = add2(a, *reinterpret_cast<const float2*>(&acc[(size_t)m * Nl + v * VEC + 2 * h]));
+              if (pass == 0) dw[j][h] = a;
+              else db[j][h] = a;
             }
           }
         }
@@ -384,45 +382,9 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
       if (v < Vl) {
         // partial rows start 256-byte aligned and N is a whole number of packets: vector stores
         const size_t o = (size_t)unit * p.N + (size_t)(v0 + v) * VEC;
-        if (p.dw_part != nullptr) st_f32_vec<VEC>(p.dw_part + o, dw[j]);
-        if (!RMS && p.db_part != nullptr) st_f32_vec<VEC>(p.db_part + o, db[j]);
+        if (p.dw_part != nullptr) st_f32_pairs<H>(p.dw_part + o, dw[j]);
+        if (!RMS && p.db_part != nullptr) st_f32_pairs<H>(p.db_part + o, db[j]);
       }
-    }
-  }
-}
-
-// Any-alignment dx kernel: one CTA per row, two scalar passes.
-template <typename T, bool RMS>
-__global__ void __launch_bounds__(256) norm_bwd_dx_any_kernel(const BwdParams p) {
-  constexpr int NV = RMS ? 1 : 2;
-  __shared__ float red[2 * NV * 8];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int phase = 0;
-  const float inv_n = 1.f / static_cast<float>(p.N);
-  for (int64_t row = blockIdx.x; row < p.M; row += gridDim.x) {
-    const T* xrow = static_cast<const T*>(p.x) + row * p.x_stride;
-    const T* grow = static_cast<const T*>(p.dy) + row * p.dy_stride;
-    T* dxrow = static_cast<T*>(p.dx) + row * p.dx_stride;
-    const float mu = RMS ? 0.f : p.mean[row];
-    const float rs = p.rstd[row];
-    float s[NV];
-#pragma unroll
-    for (int i = 0; i < NV; ++i) s[i] = 0.f;
-    for (int c = threadIdx.x; c < p.N; c += 256) {
-      const float xh = (to_f32(xrow[c]) - mu) * rs;
-      const float wv = (p.w != nullptr) ? load_param(p.w, p.w_dtype, c) : 1.f;
-      const float wdy = wv * to_f32(grow[c]);
-      s[0] += xh * wdy;
-      if (!RMS) s[NV - 1] += wdy;
-    }
-    group_sum<8, NV>(s, red, phase, -1, warp, lane);
-    const float c1 = s[0] * inv_n;
-    const float c2 = RMS ? 0.f : s[NV - 1] * inv_n;
-    for (int c = threadIdx.x; c < p.N; c += 256) {
-      const float xh = (to_f32(xrow[c]) - mu) * rs;
-      const float wv = (p.w != nullptr) ? load_param(p.w, p.w_dtype, c) : 1.f;
-      const float wdy = wv * to_f32(grow[c]);
-      dxrow[c] = from_f32<T>((wdy - (xh * c1 + c2)) * rs);
     }
   }
 }
@@ -441,6 +403,7 @@ __global__ void __launch_bounds__(256) norm_bwd_dwdb_any_kernel(const BwdParams 
   const int64_t r0 = min(shard_begin + q * chunk, shard_end);
   const int64_t r1 = min(r0 + chunk, shard_end);
   float dw = 0.f, db = 0.f;
+#pragma unroll 8
   for (int64_t r = r0; r < r1; ++r) {
     const float g = to_f32(static_cast<const T*>(p.dy)[r * p.dy_stride + col]);
     const float mu = RMS ? 0.f : p.mean[r];

@@ -36,7 +36,15 @@ __global__ void __launch_bounds__(512) colreduce_kernel(const ColReduceParams p)
     float s = 0.f;
     if (live) {
       const float* base = part + (size_t)g * p.per_shard * p.N + col;
-      for (int r = ty; r < p.per_shard; r += 16) s += base[(size_t)r * p.N];
+      // four rows requested at a time, added in row order
+      for (int r = ty; r < p.per_shard; r += 64) {
+        float v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = (r + 16 * k < p.per_shard) ? base[(size_t)(r + 16 * k) * p.N] : 0.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (r + 16 * k < p.per_shard) s += v[k];
+      }
     }
     tile[ty][tx] = s;
     __syncthreads();
@@ -69,9 +77,16 @@ __global__ void __launch_bounds__(512) colreduce4_kernel(const ColReduceParams p
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
     if (live) {
       const float* base = part + (size_t)g * p.per_shard * p.N + col;
-      for (int r = ty; r < p.per_shard; r += 16) {
-        const float4 v = *reinterpret_cast<const float4*>(base + (size_t)r * p.N);
-        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+      // four rows requested at a time, added in row order
+      for (int r = ty; r < p.per_shard; r += 64) {
+        float4 v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          v[k] = (r + 16 * k < p.per_shard) ? *reinterpret_cast<const float4*>(base + (size_t)(r + 16 * k) * p.N)
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (r + 16 * k < p.per_shard) { s.x += v[k].x; s.y += v[k].y; s.z += v[k].z; s.w += v[k].w; }
       }
     }
     tile[ty][tx] = s;

@@ -13,7 +13,18 @@ namespace b200norm {
 enum : int { kF32 = 0, kF16 = 1, kBF16 = 2, kF64 = 3 };
 
 // ---------------------------------------------------------------------------------------
-// Pack16<T>: one 128-bit packet of T and its fp32 view.
+// Packed fp32 arithmetic: sm_100 executes fma / mul / add on two fp32 values held in a register pair
+// as ONE instruction, each lane rounded exactly like the scalar instruction.  The row kernels keep
+// their per-element values as such pairs, which nearly halves the arithmetic instructions of
+// kernels that are bound by instruction issue rather than by memory.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float2 splat2(float a) { return make_float2(a, a); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+
+// ---------------------------------------------------------------------------------------
+// Pack16<T>: one 128-bit packet of T and its fp32 view (kElems floats, or kElems / 2 pairs).
 // ---------------------------------------------------------------------------------------
 template <typename T>
 struct Pack16;
@@ -30,6 +41,14 @@ struct Pack16<float> {
   __device__ __forceinline__ static uint4 pack(const float* f) {
     return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]),
                       __float_as_uint(f[3]));
+  }
+  __device__ __forceinline__ static void unpack2(const uint4& v, float2* f) {
+    f[0] = make_float2(__uint_as_float(v.x), __uint_as_float(v.y));
+    f[1] = make_float2(__uint_as_float(v.z), __uint_as_float(v.w));
+  }
+  __device__ __forceinline__ static uint4 pack2(const float2* f) {
+    return make_uint4(__float_as_uint(f[0].x), __float_as_uint(f[0].y), __float_as_uint(f[1].x),
+                      __float_as_uint(f[1].y));
   }
 };
 
@@ -51,6 +70,20 @@ struct Pack16<__half> {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  __device__ __forceinline__ static void unpack2(const uint4& v, float2* f) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f[i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+  }
+  __device__ __forceinline__ static uint4 pack2(const float2* f) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __half2 h = __float22half2_rn(f[i]);
       w[i] = *reinterpret_cast<uint32_t*>(&h);
     }
     return make_uint4(w[0], w[1], w[2], w[3]);
@@ -78,6 +111,20 @@ struct Pack16<__nv_bfloat16> {
     }
     return make_uint4(w[0], w[1], w[2], w[3]);
   }
+  __device__ __forceinline__ static void unpack2(const uint4& v, float2* f) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+  }
+  __device__ __forceinline__ static uint4 pack2(const float2* f) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(f[i].x, f[i].y);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
 };
 
 template <>
@@ -91,6 +138,15 @@ struct Pack16<double> {
     const double a = static_cast<double>(f[0]), b = static_cast<double>(f[1]);
     return make_uint4(static_cast<uint32_t>(__double2loint(a)), static_cast<uint32_t>(__double2hiint(a)),
                       static_cast<uint32_t>(__double2loint(b)), static_cast<uint32_t>(__double2hiint(b)));
+  }
+  __device__ __forceinline__ static void unpack2(const uint4& v, float2* f) {
+    float t[2];
+    unpack(v, t);
+    f[0] = make_float2(t[0], t[1]);
+  }
+  __device__ __forceinline__ static uint4 pack2(const float2* f) {
+    const float t[2] = {f[0].x, f[0].y};
+    return pack(t);
   }
 };
 
@@ -168,6 +224,117 @@ __device__ __forceinline__ void load_param_packet(const void* p, int dtype, int 
   }
 }
 
+// The parameter values that line up with a thread's packets, for up to two parameter vectors of one
+// storage type (weight and bias; a null pointer is skipped): packets v0 + j * stride + t (j < LDGS)
+// of a row of T whose part handled here is `limit` packets long; `take(j)` says which of them this
+// thread fetches.  ALL loads are issued before any value is used, so the whole set costs one trip to
+// memory -- a loop that loads and converts packet by packet pays one trip per packet, which for a
+// CTA with a few dozen rows is a visible share of its life.  `issued()` runs between the loads and
+// their first use: the kernels start their bulk row copies there, BEHIND the small parameter
+// requests, which would otherwise queue up after hundreds of kilobytes of row data.  Vector loads
+// when the storage type and alignment allow (same type as the rows; fp32 parameters with 16-bit
+// rows; 16-bit parameters with fp32 rows), element loads otherwise.  `sink(which, j, values)`
+// receives each packet of vector `which`.
+template <typename T, int LDGS, typename Take, typename Issued, typename Sink>
+__device__ __forceinline__ void load_param_packets(const void* p0, const void* p1, int dtype, int v0, int t,
+                                                   int stride, int limit, Take take, Issued issued, Sink sink) {
+  constexpr int VEC = Pack16<T>::kElems;
+  const void* const ptr[2] = {p0, p1};
+  const uintptr_t addr = reinterpret_cast<uintptr_t>(p0) | reinterpret_cast<uintptr_t>(p1);
+  if (dtype == DTypeOf<T>::value && (addr & 15u) == 0) {
+    uint4 raw[2][LDGS];
+#pragma unroll
+    for (int w = 0; w < 2; ++w)
+#pragma unroll
+      for (int j = 0; j < LDGS; ++j) {
+        const int v = j * stride + t;
+        if (ptr[w] != nullptr && v < limit && take(j)) raw[w][j] = __ldg(static_cast<const uint4*>(ptr[w]) + v0 + v);
+      }
+    issued();
+#pragma unroll
+    for (int w = 0; w < 2; ++w)
+#pragma unroll
+      for (int j = 0; j < LDGS; ++j) {
+        const int v = j * stride + t;
+        if (ptr[w] != nullptr && v < limit && take(j)) {
+          float f[VEC];
+          Pack16<T>::unpack(raw[w][j], f);
+          sink(w, j, f);
+        }
+      }
+  } else if (dtype == kF32 && VEC == 8 && (addr & 15u) == 0) {  // fp32 parameters, 16-bit rows
+    float4 raw[2][LDGS][2];
+#pragma unroll
+    for (int w = 0; w < 2; ++w)
+#pragma unroll
+      for (int j = 0; j < LDGS; ++j) {
+        const int v = j * stride + t;
+        if (ptr[w] != nullptr && v < limit && take(j)) {
+          raw[w][j][0] = __ldg(static_cast<const float4*>(ptr[w]) + (size_t)(v0 + v) * 2);
+          raw[w][j][1] = __ldg(static_cast<const float4*>(ptr[w]) + (size_t)(v0 + v) * 2 + 1);
+        }
+      }
+    issued();
+#pragma unroll
+    for (int w = 0; w < 2; ++w)
+#pragma unroll
+      for (int j = 0; j < LDGS; ++j) {
+        const int v = j * stride + t;
+        if (ptr[w] != nullptr && v < limit && take(j)) {
+          const float f[8] = {raw[w][j][0].x, raw[w][j][0].y, raw[w][j][0].z, raw[w][j][0].w,
+                              raw[w][j][1].x, raw[w][j][1].y, raw[w][j][1].z, raw[w][j][1].w};
+          sink(w, j, f);
+        }
+      }
+  } else if ((dtype == kF16 || dtype == kBF16) && VEC == 4 && (addr & 7u) == 0) {  // 16-bit parameters, fp32 rows
+    uint2 raw[2][LDGS];
+#pragma unroll
+    for (int w = 0; w < 2; ++w)
+#pragma unroll
+      for (int j = 0; j < LDGS; ++j) {
+        const int v = j * stride + t;
+        if (ptr[w] != nullptr && v < limit && take(j)) raw[w][j] = __ldg(static_cast<const uint2*>(ptr[w]) + v0 + v);
+      }
+    issued();
+#pragma unroll
+    for (int w = 0; w < 2; ++w)
+#pragma unroll
+      for (int j = 0; j < LDGS; ++j) {
+        const int v = j * stride + t;
+        if (ptr[w] != nullptr && v < limit && take(j)) {
+          float f[VEC > 4 ? VEC : 4];
+          const uint32_t w2[2] = {raw[w][j].x, raw[w][j].y};
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            if (dtype == kBF16) {
+              f[2 * i] = __uint_as_float(w2[i] << 16);
+              f[2 * i + 1] = __uint_as_float(w2[i] & 0xffff0000u);
+            } else {
+              const float2 h = __half22float2(*reinterpret_cast<const __half2*>(&w2[i]));
+              f[2 * i] = h.x;
+              f[2 * i + 1] = h.y;
+            }
+          }
+          sink(w, j, f);
+        }
+      }
+  } else {
+    issued();
+#pragma unroll
+    for (int w = 0; w < 2; ++w)
+#pragma unroll
+      for (int j = 0; j < LDGS; ++j) {
+        const int v = j * stride + t;
+        if (ptr[w] != nullptr && v < limit && take(j)) {
+          float f[VEC];
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) f[e] = load_param(ptr[w], dtype, (int64_t)(v0 + v) * VEC + e);
+          sink(w, j, f);
+        }
+      }
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // Streaming 128-bit global accesses.  x, dy, y and dx are touched exactly once per kernel, so
 // they bypass L1 on the way in and are marked evict-first on the way out; that keeps L1 for
@@ -201,6 +368,21 @@ __device__ __forceinline__ void st_f32_vec(float* p, const float* v) {
   } else {
 #pragma unroll
     for (int e = 0; e < VEC; ++e) p[e] = v[e];
+  }
+}
+
+// The same for H pairs (2 * H consecutive values).
+template <int H>
+__device__ __forceinline__ void st_f32_pairs(float* p, const float2* v) {
+  if constexpr (H == 4) {
+    asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "f"(v[0].x), "f"(v[0].y), "f"(v[1].x),
+                 "f"(v[1].y), "f"(v[2].x), "f"(v[2].y), "f"(v[3].x), "f"(v[3].y)
+                 : "memory");
+  } else if constexpr (H == 2) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0].x, v[0].y, v[1].x, v[1].y);
+  } else {
+#pragma unroll
+    for (int h = 0; h < H; ++h) *reinterpret_cast<float2*>(p + 2 * h) = v[h];
   }
 }
 

@@ -95,8 +95,8 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
   grid_dependency_sync();  // nothing above reads global memory
   trigger_dependents();
   if (CL > 1) cluster_sync_all();  // the partner CTA is running: its shared memory may be written
-  if (STAGES > 0) {
-    if (t == 0) {
+  auto first_fills = [&]() {  // the group leader requests the first STAGES rows
+    if (STAGES > 0 && t == 0) {
 #pragma unroll
       for (int s = 0; s < STAGES; ++s) {
         const int64_t r = first + s * step;
@@ -106,37 +106,33 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
         }
       }
     }
-  }
+  };
 
+  // Per-element values live as fp32 pairs (two per instruction, norm_common.cuh): H pairs per packet.
+  constexpr int H = VEC / 2;
   constexpr int PL = PREG ? LDGS : 1;
-  float wr[PL][VEC], br[PL][VEC];
+  float2 wr[PL][H], br[PL][H];
 #pragma unroll
   for (int j = 0; j < PL; ++j) {
-    const int v = j * TPR + t;
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) {
-      wr[j][e] = 1.f;
-      br[j][e] = 0.f;
+    for (int h = 0; h < H; ++h) {
+      wr[j][h] = splat2(1.f);
+      br[j][h] = splat2(0.f);
     }
-    if (PREG && v < Vl) {
-      // whole packets when the parameters are stored like the rows and 16-byte aligned
-      if (p.w != nullptr) {
-        if ((reinterpret_cast<uintptr_t>(p.w) & 15u) == 0) {
-          load_param_packet<T>(p.w, p.w_dtype, v0 + v, wr[j]);
-        } else {
+  }
+  if (PREG) {
+    // weight and bias are requested first, the rows right behind them (see load_param_packets)
+    load_param_packets<T, PL>(
+        p.w, RMS ? nullptr : p.b, p.w_dtype, v0, t, TPR, Vl, [](int) { return true; }, first_fills,
+        [&](int which, int j, const float* f) {
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) wr[j][e] = load_param(p.w, p.w_dtype, (int64_t)(v0 + v) * VEC + e);
-        }
-      }
-      if (!RMS && p.b != nullptr) {
-        if ((reinterpret_cast<uintptr_t>(p.b) & 15u) == 0) {
-          load_param_packet<T>(p.b, p.w_dtype, v0 + v, br[j]);
-        } else {
-#pragma unroll
-          for (int e = 0; e < VEC; ++e) br[j][e] = load_param(p.b, p.w_dtype, (int64_t)(v0 + v) * VEC + e);
-        }
-      }
-    }
+          for (int h = 0; h < H; ++h) {
+            if (which == 0) wr[j][h] = make_float2(f[2 * h], f[2 * h + 1]);
+            else br[j][h] = make_float2(f[2 * h], f[2 * h + 1]);
+          }
+        });
+  } else {
+    first_fills();
   }
 
   const float inv_n = 1.f / static_cast<float>(p.N);
@@ -148,7 +144,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
   uint32_t parity = 0;
 
   for (int64_t row = first; row < p.M; row += step) {
-    float xf[LDGS][VEC];
+    float2 xf[LDGS][H];
     if (STAGES > 0) {
       mbar_wait(&bars[slot], parity, &cta_abort, p.status);
       const uint4* srow = reinterpret_cast<const uint4*>(slots + (size_t)slot * row_bytes);
@@ -157,7 +153,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
         const int v = j * TPR + t;
         uint4 pk = make_uint4(0, 0, 0, 0);
         if (v < Vl) pk = ld_shared16(srow + v);
-        Pack16<T>::unpack(pk, xf[j]);
+        Pack16<T>::unpack2(pk, xf[j]);
       }
     } else {
       const uint4* xrow = reinterpret_cast<const uint4*>(xb + row * p.x_stride) + v0;
@@ -166,31 +162,37 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
         const int v = j * TPR + t;
         uint4 pk = make_uint4(0, 0, 0, 0);
         if (v < Vl) pk = ld_stream(xrow + v);
-        Pack16<T>::unpack(pk, xf[j]);
+        Pack16<T>::unpack2(pk, xf[j]);
       }
     }
 
+    // Per-thread sums run as two chains (the lanes of a pair), added at the end.
     float mean = 0.f;
     float q[1] = {0.f};
+    float2 q2 = splat2(0.f);
     if (!RMS) {
-      float s[1] = {0.f};
+      float2 s2 = splat2(0.f);
 #pragma unroll
       for (int j = 0; j < LDGS; ++j)
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) s[0] += xf[j][e];
+        for (int h = 0; h < H; ++h) s2 = add2(s2, xf[j][h]);
+      float s[1] = {s2.x + s2.y};
       if (uniform) {
         // One reduction: per-thread mean and centred squares, merged with Chan's update.
         float cnt = thread_cnt;
         mean = s[0] * thread_inv_cnt;
+        const float2 nm = splat2(-mean);
 #pragma unroll
         for (int j = 0; j < LDGS; ++j) {
-          const bool live = (j * TPR + t) < Vl;
+          if ((j * TPR + t) < Vl) {
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) {
-            const float d = live ? (xf[j][e] - mean) : 0.f;
-            q[0] += d * d;
+            for (int h = 0; h < H; ++h) {
+              const float2 d = add2(xf[j][h], nm);
+              q2 = fma2(d, d, q2);
+            }
           }
         }
+        q[0] = q2.x + q2.y;
         group_moments<WARPS_N, 0>(cnt, mean, q[0], red_smem[warp_m], phase, warp_m, warp_n, lane);
         if (CL > 1) {  // merge the two halves (equal counts), rank 0's first
           const float mine[2] = {mean, q[0]};
@@ -218,7 +220,8 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
 #pragma unroll
       for (int j = 0; j < LDGS; ++j)
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) q[0] += xf[j][e] * xf[j][e];
+        for (int h = 0; h < H; ++h) q2 = fma2(xf[j][h], xf[j][h], q2);
+      q[0] = q2.x + q2.y;
       group_sum<WARPS_N, 1, 0>(q, red_smem[warp_m], phase, warp_m, warp_n, lane);
       if (CL > 1) {
         const float mine[2] = {q[0], 0.f};
@@ -242,15 +245,18 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
       }
     }
     if (!RMS && !uniform) {
+      const float2 nm = splat2(-mean);
 #pragma unroll
       for (int j = 0; j < LDGS; ++j) {
-        const bool live = (j * TPR + t) < Vl;
+        if ((j * TPR + t) < Vl) {
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-          const float d = live ? (xf[j][e] - mean) : 0.f;
-          q[0] += d * d;
+          for (int h = 0; h < H; ++h) {
+            const float2 d = add2(xf[j][h], nm);
+            q2 = fma2(d, d, q2);
+          }
         }
       }
+      q[0] = q2.x + q2.y;
       group_sum<WARPS_N, 1, 0>(q, red_smem[warp_m], phase, warp_m, warp_n, lane);
       if (CL > 1) {
         const float mine[2] = {q[0], 0.f};
@@ -265,68 +271,39 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
       p.rstd[row] = rstd;
     }
 
+    // y = (x - mean) * rstd * w + b (layernorm.py:38-45)
     uint4* yrow = reinterpret_cast<uint4*>(yb + row * p.y_stride) + v0;
+    const float2 nm = splat2(-mean), r2 = splat2(rstd);
 #pragma unroll
     for (int j = 0; j < LDGS; ++j) {
       const int v = j * TPR + t;
-      float yf[VEC];
+      float2 yf[H];
       if (PREG) {
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) yf[e] = (xf[j][e] - mean) * rstd * wr[j][e] + br[j][e];
+        for (int h = 0; h < H; ++h) yf[h] = fma2(mul2(add2(xf[j][h], nm), r2), wr[j][h], br[j][h]);
       } else if (v < Vl) {
-        if (p.w != nullptr) load_param_packet<T>(p.w, p.w_dtype, v0 + v, wr[0]);
-        if (!RMS && p.b != nullptr) load_param_packet<T>(p.b, p.w_dtype, v0 + v, br[0]);
+        float wf[VEC], bf[VEC];
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) yf[e] = (xf[j][e] - mean) * rstd * wr[0][e] + br[0][e];
+        for (int e = 0; e < VEC; ++e) {
+          wf[e] = 1.f;
+          bf[e] = 0.f;
+        }
+        if (p.w != nullptr) load_param_packet<T>(p.w, p.w_dtype, v0 + v, wf);
+        if (!RMS && p.b != nullptr) load_param_packet<T>(p.b, p.w_dtype, v0 + v, bf);
+#pragma unroll
+        for (int h = 0; h < H; ++h)
+          yf[h] = fma2(mul2(add2(xf[j][h], nm), r2), make_float2(wf[2 * h], wf[2 * h + 1]),
+                       make_float2(bf[2 * h], bf[2 * h + 1]));
       }
       if (ACT != kActNone && v < Vl) {
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) yf[e] = act_fwd<ACT>(yf[e]);
+        for (int h = 0; h < H; ++h) yf[h] = act_fwd2<ACT>(yf[h]);
       }
-      if (v < Vl) st_stream(yrow + v, Pack16<T>::pack(yf));
+      if (v < Vl) st_stream(yrow + v, Pack16<T>::pack2(yf));
     }
   }
   if (STAGES > 0) {
     if (t == 0 && cta_abort) drain_ring<STAGES>(bars, first < p.M ? (p.M - first + step - 1) / step : 0);
-  }
-}
-
-// Any-alignment kernel: one CTA per row, scalar accesses, three passes over the row (the
-// second and third hit L1/L2).  Serves rows whose length, base address or stride is not a
-// multiple of 16 bytes.
-template <typename T, bool RMS>
-__global__ void __launch_bounds__(256) norm_fwd_any_kernel(const FwdParams p) {
-  __shared__ float red[2][8];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int phase = 0;
-  const float inv_n = 1.f / static_cast<float>(p.N);
-  for (int64_t row = blockIdx.x; row < p.M; row += gridDim.x) {
-    const T* xrow = static_cast<const T*>(p.x) + row * p.x_stride;
-    T* yrow = static_cast<T*>(p.y) + row * p.y_stride;
-    float mean = 0.f;
-    if (!RMS) {
-      float s[1] = {0.f};
-      for (int c = threadIdx.x; c < p.N; c += 256) s[0] += to_f32(xrow[c]);
-      group_sum<8, 1>(s, &red[0][0], phase, -1, warp, lane);
-      mean = s[0] * inv_n;
-    }
-    float q[1] = {0.f};
-    for (int c = threadIdx.x; c < p.N; c += 256) {
-      const float d = to_f32(xrow[c]) - mean;
-      q[0] += d * d;
-    }
-    group_sum<8, 1>(q, &red[0][0], phase, -1, warp, lane);
-    const float rstd = 1.f / sqrtf(q[0] * inv_n + p.eps);
-    if (threadIdx.x == 0) {
-      if (!RMS) p.mean[row] = mean;
-      p.rstd[row] = rstd;
-    }
-    for (int c = threadIdx.x; c < p.N; c += 256) {
-      float yv = (to_f32(xrow[c]) - mean) * rstd;
-      if (p.w != nullptr) yv *= load_param(p.w, p.w_dtype, c);
-      if (!RMS && p.b != nullptr) yv += load_param(p.b, p.w_dtype, c);
-      yrow[c] = from_f32<T>(yv);
-    }
   }
 }
 

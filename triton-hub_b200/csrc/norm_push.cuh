@@ -197,12 +197,24 @@ __global__ void __launch_bounds__(512) colreduce_push_kernel(const ColReducePush
       for (int e = 0; e < W; ++e) s[e] = 0.f;
       if (live) {
         const float* base = part + (size_t)g * p.per_shard * p.N + col;
-        for (int r = ty; r < p.per_shard; r += 16) {
+        // four rows requested at a time, added in row order
+        for (int r = ty; r < p.per_shard; r += 64) {
           if constexpr (W == 4) {
-            const float4 v = *reinterpret_cast<const float4*>(base + (size_t)r * p.N);
-            s[0] += v.x; s[1] += v.y; s[2] += v.z; s[3] += v.w;
+            float4 v[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              v[k] = (r + 16 * k < p.per_shard) ? *reinterpret_cast<const float4*>(base + (size_t)(r + 16 * k) * p.N)
+                                                : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              if (r + 16 * k < p.per_shard) { s[0] += v[k].x; s[1] += v[k].y; s[2] += v[k].z; s[3] += v[k].w; }
           } else {
-            s[0] += base[(size_t)r * p.N];
+            float v[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v[k] = (r + 16 * k < p.per_shard) ? base[(size_t)(r + 16 * k) * p.N] : 0.f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              if (r + 16 * k < p.per_shard) s[0] += v[k];
           }
         }
       }

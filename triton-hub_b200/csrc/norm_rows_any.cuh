@@ -1,0 +1,367 @@
+// LayerNorm / RMSNorm for rows of ANY alignment: a base address, row stride or row length that is
+// not a multiple of 16 bytes (odd lengths, offset views).  The reference runs such rows at full
+// speed through masked vector loads (TritonHub/Normalization/layernorm.py:28-46, `cols < N`); the
+// packet kernels cannot (their threads own fixed 16-byte packets), so these kernels stage each
+// row through shared memory instead:
+//
+//   global -> shared : the row's aligned 16-byte interior by ONE bulk asynchronous copy completed
+//                      on an mbarrier (norm_stage.cuh), the few elements before and after it one
+//                      by one; the row lands at the same offset within a 16-byte line as in global
+//                      memory, so element i sits at a fixed place whatever the row's alignment.
+//                      A ring of up to four such slots per CTA keeps that many rows in flight;
+//   shared -> regs   : thread t takes elements t, t + THREADS, ... (K of them) -- one trip to
+//                      global memory per row, the passes after that run on registers;
+//   regs -> shared -> global : the result row is laid out at ITS alignment and written back with
+//                      128-bit stores for the interior.
+//
+// One CTA works on one row at a time and walks the rows grid-strided.  Forward: statistics by the
+// reference's two passes (mean, then centred squares).  Backward: dx here, dweight / dbias by the
+// column kernel in norm_bwd.cuh.  Every mbarrier wait is bounded like in the packet kernels.
+#pragma once
+
+#include "norm_bwd.cuh"
+#include "norm_fwd.cuh"
+
+namespace b200norm {
+
+constexpr int kRowStagesMax = 4;
+
+__device__ __forceinline__ uint32_t dynamic_smem_bytes() {
+  uint32_t n;
+  asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(n));
+  return n;
+}
+
+// How a row of `n` elements of T at `ptr` (any alignment) splits into the elements before the first
+// 16-byte boundary, the aligned interior and the elements after it.  In a slot, element i lives at
+// slot + phase + i * sizeof(T); a slot is 16-byte aligned and holds n * sizeof(T) + 16 bytes.
+// Last step of a CTA whose bounded wait ran out: copies it issued may still be in flight, so the
+// leader lingers 10 ms before the CTA's shared memory is released (the packet kernels wait on
+// their ring's barriers instead; here the number of slots is a run-time value).
+__device__ __forceinline__ void linger_after_abort() {
+  const unsigned long long t0 = global_ns();
+  while (global_ns() - t0 < 10000000ull) {
+  }
+}
+
+template <typename T>
+struct RowSpan {
+  int phase, head, body_bytes, tail0;
+  __device__ __forceinline__ RowSpan(const T* ptr, int n) {
+    constexpr int ES = static_cast<int>(sizeof(T));
+    phase = static_cast<int>(reinterpret_cast<uintptr_t>(ptr) & 15u);
+    head = min(n, ((16 - phase) & 15) / ES);   // elements before the first 16-byte boundary
+    const int body = (n - head) * ES / 16;     // whole 16-byte packets after them
+    body_bytes = body * 16;
+    tail0 = head + body * (16 / ES);           // first element after the packets
+  }
+};
+
+template <typename T>
+__device__ __forceinline__ void copy_row_edges(unsigned char* shm, const T* src, int n, const RowSpan<T>& sp, int tid,
+                                               int nthreads) {
+  T* dst = reinterpret_cast<T*>(shm + sp.phase);
+  if (tid < sp.head) dst[tid] = src[tid];
+  for (int i = sp.tail0 + tid; i < n; i += nthreads) dst[i] = src[i];
+}
+
+// The mirror image: `n` elements laid out in shared memory at the phase of `dst` go to global memory.
+template <typename T>
+__device__ __forceinline__ void stage_row_out(const unsigned char* shm, T* dst, int n, int tid, int nthreads) {
+  constexpr int ES = static_cast<int>(sizeof(T));
+  const uintptr_t start = reinterpret_cast<uintptr_t>(dst);
+  const int phase = static_cast<int>(start & 15u);
+  const int head = min(n, ((16 - phase) & 15) / ES);
+  const int body = (n - head) * ES / 16;
+  const int tail0 = head + body * (16 / ES);
+  const T* src = reinterpret_cast<const T*>(shm + phase);
+  uint4* gdst = reinterpret_cast<uint4*>(dst + head);
+  const uint4* ssrc = reinterpret_cast<const uint4*>(shm + phase + head * ES);
+  for (int v = tid; v < body; v += nthreads) st_stream(gdst + v, ssrc[v]);
+  if (tid < head) dst[tid] = src[tid];
+  for (int i = tail0 + tid; i < n; i += nthreads) dst[i] = src[i];
+}
+
+// Parameter values of the columns tid, tid + nthreads, ... (K of them), `fill` past the end or
+// without a parameter vector.  The storage type is switched on once, outside the loop, so that the
+// K loads are issued together.
+template <int K>
+__device__ __forceinline__ void load_param_columns(const void* p, int dtype, int tid, int nthreads, int n, float fill,
+                                                   float (&out)[K]) {
+#pragma unroll
+  for (int k = 0; k < K; ++k) out[k] = fill;
+  if (p == nullptr) return;
+  switch (dtype) {
+    case kF32:
+#pragma unroll
+      for (int k = 0; k < K; ++k)
+        if (tid + k * nthreads < n) out[k] = __ldg(static_cast<const float*>(p) + tid + k * nthreads);
+      break;
+    case kF16:
+#pragma unroll
+      for (int k = 0; k < K; ++k)
+        if (tid + k * nthreads < n) out[k] = __half2float(__ldg(static_cast<const __half*>(p) + tid + k * nthreads));
+      break;
+    case kBF16:
+#pragma unroll
+      for (int k = 0; k < K; ++k)
+        if (tid + k * nthreads < n)
+          out[k] = __bfloat162float(__ldg(static_cast<const __nv_bfloat16*>(p) + tid + k * nthreads));
+      break;
+    default:
+#pragma unroll
+      for (int k = 0; k < K; ++k)
+        if (tid + k * nthreads < n) out[k] = static_cast<float>(__ldg(static_cast<const double*>(p) + tid + k * nthreads));
+      break;
+  }
+}
+
+// Dynamic shared memory of these kernels: `rows` row buffers of row_buffer_bytes(N, sizeof(T)) each.
+__host__ __device__ inline size_t row_buffer_bytes(int64_t N, int es) {
+  return (static_cast<size_t>(N) * es + 16 + 15) & ~static_cast<size_t>(15);
+}
+
+// Forward.  THREADS * K >= N.  PREG: weight and bias sit in registers for the life of the CTA;
+// without it (1024 threads leave 64 registers each) they are re-read per row, eight columns at a time.
+// Dynamic shared memory: (stages + 1) row buffers -- the ring, then the output row.
+template <typename T, int THREADS, int K, bool PREG, bool RMS>
+__global__ void __launch_bounds__(THREADS) norm_fwd_row_kernel(const FwdParams p) {
+  constexpr int WARPS = THREADS / 32;
+  constexpr int ES = static_cast<int>(sizeof(T));
+  extern __shared__ __align__(128) unsigned char dyn_smem[];
+  __shared__ float red[2 * WARPS];
+  __shared__ __align__(8) uint64_t full_bar[kRowStagesMax];
+  __shared__ int cta_abort;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const size_t buf = row_buffer_bytes(p.N, ES);
+  const int stages = min(kRowStagesMax, static_cast<int>(dynamic_smem_bytes() / buf) - 1);
+  unsigned char* s_out = dyn_smem + (size_t)stages * buf;
+  int phase_bit = 0;
+  const T* xb = static_cast<const T*>(p.x);
+
+  auto fill = [&](int slot, int64_t row) {  // every thread calls it; the leader arms the barrier and copies
+    const T* xrow = xb + row * p.x_stride;
+    const RowSpan<T> sp(xrow, p.N);
+    unsigned char* shm = dyn_smem + (size_t)slot * buf;
+    if (tid == 0) {
+      mbar_expect_tx(&full_bar[slot], static_cast<uint32_t>(sp.body_bytes));
+      if (sp.body_bytes > 0)
+        bulk_load(shm + sp.phase + sp.head * ES, xrow + sp.head, static_cast<uint32_t>(sp.body_bytes), &full_bar[slot]);
+    }
+    copy_row_edges<T>(shm, xrow, p.N, sp, tid, THREADS);
+  };
+
+  if (tid == 0) {
+    for (int i = 0; i < kRowStagesMax; ++i) mbar_init(&full_bar[i], 1);
+    cta_abort = 0;
+    mbar_init_fence();
+  }
+  __syncthreads();
+  constexpr int PK = PREG ? K : 1;
+  constexpr int CH = K < 8 ? K : 8;  // columns per parameter chunk without PREG
+  float wr[PK], br[PK];
+  if (PREG) {
+    load_param_columns<PK>(p.w, p.w_dtype, tid, THREADS, p.N, 1.f, wr);
+    load_param_columns<PK>(RMS ? nullptr : p.b, p.w_dtype, tid, THREADS, p.N, 0.f, br);
+  }
+  for (int s = 0; s < stages; ++s) {
+    const int64_t r = (int64_t)blockIdx.x + (int64_t)s * gridDim.x;
+    if (r < p.M) fill(s, r);
+  }
+  __syncthreads();  // the edge elements of the first rows are in place
+  const float inv_n = 1.f / static_cast<float>(p.N);
+  int slot = 0;
+  uint32_t parity = 0;
+  for (int64_t row = blockIdx.x; row < p.M; row += gridDim.x) {
+    T* yrow = static_cast<T*>(p.y) + row * p.y_stride;
+    mbar_wait(&full_bar[slot], parity, &cta_abort, p.status);
+    const T* xs = reinterpret_cast<const T*>(dyn_smem + (size_t)slot * buf +
+                                             (reinterpret_cast<uintptr_t>(xb + row * p.x_stride) & 15u));
+    float xv[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int c = tid + k * THREADS;
+      xv[k] = c < p.N ? to_f32(xs[c]) : 0.f;
+    }
+    // The first reduction of a row is also the point after which every thread holds its elements in
+    // registers (its barrier covers the whole CTA): the slot can take the row `stages` rows ahead.
+    auto refill = [&]() {
+      const int64_t r = row + (int64_t)stages * gridDim.x;
+      if (r < p.M) fill(slot, r);
+      if (++slot == stages) {
+        slot = 0;
+        parity ^= 1u;
+      }
+    };
+    float mean = 0.f;
+    if (!RMS) {
+      float s[1] = {0.f};
+#pragma unroll
+      for (int k = 0; k < K; ++k) s[0] += xv[k];
+      group_sum<WARPS, 1, 0>(s, red, phase_bit, 0, warp, lane);
+      refill();
+      mean = s[0] * inv_n;
+    }
+    float q[1] = {0.f};
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const float d = (tid + k * THREADS) < p.N ? xv[k] - mean : 0.f;
+      q[0] += d * d;
+    }
+    group_sum<WARPS, 1, 0>(q, red, phase_bit, 0, warp, lane);
+    if (RMS) refill();
+    const float rstd = 1.f / sqrtf(q[0] * inv_n + p.eps);
+    if (tid == 0) {
+      if (!RMS) p.mean[row] = mean;
+      p.rstd[row] = rstd;
+    }
+    T* ys = reinterpret_cast<T*>(s_out + static_cast<int>(reinterpret_cast<uintptr_t>(yrow) & 15u));
+    if (PREG) {
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const int c = tid + k * THREADS;
+        if (c < p.N) ys[c] = from_f32<T>((xv[k] - mean) * rstd * wr[PREG ? k : 0] + br[PREG ? k : 0]);
+      }
+    } else {
+#pragma unroll
+      for (int k0 = 0; k0 < K; k0 += CH) {
+        float wc[CH], bc[CH];
+        load_param_columns<CH>(p.w, p.w_dtype, tid + k0 * THREADS, THREADS, p.N, 1.f, wc);
+        load_param_columns<CH>(RMS ? nullptr : p.b, p.w_dtype, tid + k0 * THREADS, THREADS, p.N, 0.f, bc);
+#pragma unroll
+        for (int k = 0; k < CH; ++k) {
+          const int c = tid + (k0 + k) * THREADS;
+          if (c < p.N) ys[c] = from_f32<T>((xv[k0 + k] - mean) * rstd * wc[k] + bc[k]);
+        }
+      }
+    }
+    __syncthreads();
+    stage_row_out<T>(s_out, yrow, p.N, tid, THREADS);
+    // s_out is written again only after the next row's first reduction, whose barrier every thread
+    // reaches after its part of this copy-out.
+  }
+  if (tid == 0 && cta_abort) linger_after_abort();
+}
+
+// Backward, dx only.  THREADS * K >= N.  FAT (256 threads): the weights sit in registers and xhat and
+// w*dy stay there between the two passes; otherwise (1024 threads, 64 registers each) the weights
+// are re-read per row, eight columns at a time, and pass 2 recomputes from the staged rows.
+// Dynamic shared memory: (2 * stages + 1) row buffers -- the ring of (x, dy) pairs, then the output row.
+template <typename T, int THREADS, int K, bool FAT, bool RMS>
+__global__ void __launch_bounds__(THREADS) norm_bwd_dx_row_kernel(const BwdParams p) {
+  constexpr int WARPS = THREADS / 32;
+  constexpr int NV = RMS ? 1 : 2;
+  constexpr int ES = static_cast<int>(sizeof(T));
+  extern __shared__ __align__(128) unsigned char dyn_smem[];
+  __shared__ float red[2 * NV * WARPS];
+  __shared__ __align__(8) uint64_t full_bar[kRowStagesMax];
+  __shared__ int cta_abort;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const size_t buf = row_buffer_bytes(p.N, ES);
+  const int stages = min(kRowStagesMax, (static_cast<int>(dynamic_smem_bytes() / buf) - 1) / 2);
+  unsigned char* s_out = dyn_smem + (size_t)2 * stages * buf;
+  int phase_bit = 0;
+  const T* xb = static_cast<const T*>(p.x);
+  const T* gb = static_cast<const T*>(p.dy);
+
+  auto fill = [&](int slot, int64_t row) {
+    const T* xrow = xb + row * p.x_stride;
+    const T* grow = gb + row * p.dy_stride;
+    const RowSpan<T> sx(xrow, p.N), sg(grow, p.N);
+    unsigned char* shx = dyn_smem + (size_t)(2 * slot) * buf;
+    unsigned char* shg = shx + buf;
+    if (tid == 0) {
+      mbar_expect_tx(&full_bar[slot], static_cast<uint32_t>(sx.body_bytes + sg.body_bytes));
+      if (sx.body_bytes > 0)
+        bulk_load(shx + sx.phase + sx.head * ES, xrow + sx.head, static_cast<uint32_t>(sx.body_bytes), &full_bar[slot]);
+      if (sg.body_bytes > 0)
+        bulk_load(shg + sg.phase + sg.head * ES, grow + sg.head, static_cast<uint32_t>(sg.body_bytes), &full_bar[slot]);
+    }
+    copy_row_edges<T>(shx, xrow, p.N, sx, tid, THREADS);
+    copy_row_edges<T>(shg, grow, p.N, sg, tid, THREADS);
+  };
+
+  if (tid == 0) {
+    for (int i = 0; i < kRowStagesMax; ++i) mbar_init(&full_bar[i], 1);
+    cta_abort = 0;
+    mbar_init_fence();
+  }
+  __syncthreads();
+  constexpr int PK = FAT ? K : 1;
+  constexpr int CH = K < 8 ? K : 8;
+  float wr[PK];
+  if (FAT) load_param_columns<PK>(p.w, p.w_dtype, tid, THREADS, p.N, 1.f, wr);
+  for (int s = 0; s < stages; ++s) {
+    const int64_t r = (int64_t)blockIdx.x + (int64_t)s * gridDim.x;
+    if (r < p.M) fill(s, r);
+  }
+  __syncthreads();
+  const float inv_n = 1.f / static_cast<float>(p.N);
+  int slot = 0;
+  uint32_t parity = 0;
+  for (int64_t row = blockIdx.x; row < p.M; row += gridDim.x) {
+    T* dxrow = static_cast<T*>(p.dx) + row * p.dx_stride;
+    const float mu = RMS ? 0.f : __ldg(p.mean + row);
+    const float rs = __ldg(p.rstd + row);
+    mbar_wait(&full_bar[slot], parity, &cta_abort, p.status);
+    const T* xs = reinterpret_cast<const T*>(dyn_smem + (size_t)(2 * slot) * buf +
+                                             (reinterpret_cast<uintptr_t>(xb + row * p.x_stride) & 15u));
+    const T* gs = reinterpret_cast<const T*>(dyn_smem + (size_t)(2 * slot + 1) * buf +
+                                             (reinterpret_cast<uintptr_t>(gb + row * p.dy_stride) & 15u));
+    float xh_k[PK], wdy_k[PK];
+    float s[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) s[i] = 0.f;
+#pragma unroll
+    for (int k0 = 0; k0 < K; k0 += CH) {
+      float wc[CH];
+      if (!FAT) load_param_columns<CH>(p.w, p.w_dtype, tid + k0 * THREADS, THREADS, p.N, 1.f, wc);
+#pragma unroll
+      for (int k = 0; k < CH; ++k) {
+        const int c = tid + (k0 + k) * THREADS;
+        float xh = 0.f, wdy = 0.f;
+        if (c < p.N) {
+          xh = (to_f32(xs[c]) - mu) * rs;
+          wdy = (FAT ? wr[FAT ? k0 + k : 0] : wc[k]) * to_f32(gs[c]);
+        }
+        s[0] += xh * wdy;
+        if (!RMS) s[NV - 1] += wdy;
+        if (FAT) {
+          xh_k[FAT ? k0 + k : 0] = xh;
+          wdy_k[FAT ? k0 + k : 0] = wdy;
+        }
+      }
+    }
+    group_sum<WARPS, NV, 0>(s, red, phase_bit, 0, warp, lane);
+    const float c1 = s[0] * inv_n;
+    const float c2 = RMS ? 0.f : s[NV - 1] * inv_n;
+    T* os = reinterpret_cast<T*>(s_out + static_cast<int>(reinterpret_cast<uintptr_t>(dxrow) & 15u));
+#pragma unroll
+    for (int k0 = 0; k0 < K; k0 += CH) {
+      float wc[CH];
+      if (!FAT) load_param_columns<CH>(p.w, p.w_dtype, tid + k0 * THREADS, THREADS, p.N, 1.f, wc);
+#pragma unroll
+      for (int k = 0; k < CH; ++k) {
+        const int c = tid + (k0 + k) * THREADS;
+        if (c < p.N) {
+          const float xh = FAT ? xh_k[FAT ? k0 + k : 0] : (to_f32(xs[c]) - mu) * rs;
+          const float wdy = FAT ? wdy_k[FAT ? k0 + k : 0] : wc[k] * to_f32(gs[c]);
+          os[c] = from_f32<T>((wdy - (xh * c1 + c2)) * rs);
+        }
+      }
+    }
+    __syncthreads();  // the output row is complete, and every thread is done reading the slot
+    {
+      const int64_t r = row + (int64_t)stages * gridDim.x;
+      if (r < p.M) fill(slot, r);
+      if (++slot == stages) {
+        slot = 0;
+        parity ^= 1u;
+      }
+    }
+    stage_row_out<T>(s_out, dxrow, p.N, tid, THREADS);
+  }
+  if (tid == 0 && cta_abort) linger_after_abort();
+}
+
+}  // namespace b200norm

@@ -26,12 +26,21 @@ struct DTypeKernels {
   int n_fwd[2];
   const PacketKernel* bwd[2];
   int n_bwd[2];
-  const void* fwd_any[2];       // any-alignment norm kernels (tables without a fused activation only)
-  const void* bwd_dx_any[2];
+  // any-alignment norm kernels (tables without a fused activation only): rows staged through shared
+  // memory, [op][shape] with the shapes of kRowShapes below; dweight / dbias by a column kernel
+  const void* fwd_rows[2][4];
+  const void* bwd_dx_rows[2][4];
   const void* bwd_dwdb_any[2];
   const void* act_packet[2];    // stand-alone activation, [0] forward [1] backward (tables of an activation only)
   const void* act_any[2];
 };
+
+// Launch shapes of the any-alignment row kernels: the first whose threads * columns-per-thread
+// covers the row is used.
+struct RowShape {
+  int threads, columns;
+};
+constexpr RowShape kRowShapes[4] = {{256, 4}, {256, 16}, {256, 32}, {1024, 32}};
 
 // Softmax / LogSoftmax: one shape list per storage type; fn[log][bwd].
 struct SoftmaxKernel {
