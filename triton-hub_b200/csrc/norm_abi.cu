@@ -175,9 +175,9 @@ bool aligned16(const void* p, int64_t stride_elems, int es) {
 
 // Shape of the any-alignment row kernels for a row of N elements (norm_table.h).
 int row_shape(int64_t N) {
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < kRowShapeCount; ++i)
     if ((int64_t)kRowShapes[i].threads * kRowShapes[i].columns >= N) return i;
-  return 3;  // unreachable: 1024 x 32 covers the 64 KB row limit for every storage type
+  return kRowShapeCount - 1;  // unreachable: 1024 x 32 covers the 64 KB row limit for every storage type
 }
 
 // Dynamic shared memory of a backward launch, per CTA: (warps_m [+1 with a fused activation: the
@@ -245,8 +245,16 @@ int launch(const void* fn, dim3 grid, dim3 block, size_t smem, void* params, cud
 // Launches an any-alignment row kernel (forward: one staged row per ring slot, backward dx: two).
 // Shared memory per CTA = (rows_per_slot * slots + 1) row buffers; four slots when that leaves room
 // for a second CTA on the SM, else as many as fit.
-int launch_row_kernel(DeviceState& dev, const void* const (&fns)[4], int64_t M, int64_t N, int es, int rows_per_slot,
+int launch_row_kernel(DeviceState& dev, const void* const (&fns)[kRowShapeCount], const void* const (&warp_fns)[3], int64_t M, int64_t N, int es, int rows_per_slot,
                       void* params, cudaStream_t stream) {
+  if (N <= kWarpRowSizes[2]) {  // short rows: one warp per row, eight rows per CTA, no shared memory
+    const void* fn = warp_fns[N <= kWarpRowSizes[0] ? 0 : N <= kWarpRowSizes[1] ? 1 : 2];
+    int occ;
+    if (int rc = occupancy(dev, fn, kWarpRowWarps * 32, 0, &occ)) return rc;
+    const int64_t want = (M + kWarpRowWarps - 1) / kWarpRowWarps;
+    const int grid = static_cast<int>(std::min<int64_t>(want, (int64_t)dev.sm_count * occ));
+    return launch(fn, dim3(grid), dim3(kWarpRowWarps * 32), 0, params, stream, false);
+  }
   const int shape = row_shape(N);
   const void* fn = fns[shape];
   const int threads = kRowShapes[shape].threads;
@@ -314,7 +322,7 @@ int fwd_impl(int op, const void* x, int64_t xs, const void* w, const void* b, vo
     return fail(B200NORM_ERR_UNSUPPORTED,
                 "a fused activation needs rows whose base, stride and length are multiples of 16 bytes; run the norm "
                 "and b200norm_gelu_fwd separately");
-  return launch_row_kernel(*dev, k->fwd_rows[op], M, N, es, 1, &p, static_cast<cudaStream_t>(stream));
+  return launch_row_kernel(*dev, k->fwd_rows[op], k->fwd_warp_rows[op], M, N, es, 1, &p, static_cast<cudaStream_t>(stream));
 }
 
 // How a backward call is laid out: which kernel, how many partial rows.
@@ -324,8 +332,13 @@ struct BwdPlan {
   size_t smem;
 };
 
-int any_ctas_per_shard(int64_t rows_per_shard) {
-  return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(256, (rows_per_shard + 63) / 64)));
+// Partial rows per shard of the any-alignment dweight / dbias kernel (one thread per column, one CTA
+// per 256 columns and partial row): enough CTAs to fill the GPU twice over whatever the row length,
+// at least 32 rows each.  A function of the shard's shape only, so the order of additions is fixed.
+int any_ctas_per_shard(int64_t rows_per_shard, int64_t N) {
+  const int64_t column_blocks = (N + 255) / 256;
+  const int64_t want = (2368 + column_blocks - 1) / column_blocks;
+  return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(want, 2048), (rows_per_shard + 31) / 32)));
 }
 
 int plan_bwd(DeviceState& dev, const DTypeKernels* k, int op, int64_t rows_per_shard, int64_t N, bool packets,
@@ -333,7 +346,7 @@ int plan_bwd(DeviceState& dev, const DTypeKernels* k, int op, int64_t rows_per_s
   const int es = k->elem_size;
   plan->pk = packets ? pick(k->bwd[op], k->n_bwd[op], N * es / 16, true, N, es, act) : nullptr;
   if (plan->pk == nullptr) {
-    plan->ctas_per_shard = any_ctas_per_shard(rows_per_shard);
+    plan->ctas_per_shard = any_ctas_per_shard(rows_per_shard, N);
     plan->smem = 0;
     return B200NORM_OK;
   }
@@ -456,7 +469,7 @@ int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, con
       return rc;
   } else {
     if (M > 0) {
-      if (int rc = launch_row_kernel(*dev, k->bwd_dx_rows[op], M, N, es, 2, &p, stream)) return rc;
+      if (int rc = launch_row_kernel(*dev, k->bwd_dx_rows[op], k->bwd_dx_warp_rows[op], M, N, es, 2, &p, stream)) return rc;
     }
     if (want_params) {
       const dim3 grid(static_cast<unsigned>((N + 255) / 256), static_cast<unsigned>(P));
@@ -727,7 +740,7 @@ int rms_bwd_static_impl(const void* x, int64_t xs, const void* dy, int64_t dys, 
       return rc;
   } else {
     if (M > 0) {
-      if (int rc = launch_row_kernel(*dev, k->bwd_dx_rows[kRMS], M, N, es, 2, &p, stream)) return rc;
+      if (int rc = launch_row_kernel(*dev, k->bwd_dx_rows[kRMS], k->bwd_dx_warp_rows[kRMS], M, N, es, 2, &p, stream)) return rc;
     }
     if (dw != nullptr) {
       const dim3 grid(static_cast<unsigned>((N + 255) / 256), static_cast<unsigned>(P));
@@ -779,7 +792,7 @@ size_t b200norm_bwd_workspace_bytes(int64_t M, int64_t N, int io_dtype, int row_
   if (device_state(&dev)) return 0;
   const DTypeKernels* k = kernels_for(io_dtype);
   const int64_t rps = M / row_shards;
-  int64_t per_shard = any_ctas_per_shard(rps);
+  int64_t per_shard = any_ctas_per_shard(rps, N);
   if ((N * k->elem_size) % 16 == 0) {
     // LayerNorm and RMSNorm instantiations may differ in occupancy: take the larger.
     // and with or without a fused activation

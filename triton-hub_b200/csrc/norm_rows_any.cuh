@@ -125,7 +125,7 @@ __host__ __device__ inline size_t row_buffer_bytes(int64_t N, int es) {
 // without it (1024 threads leave 64 registers each) they are re-read per row, eight columns at a time.
 // Dynamic shared memory: (stages + 1) row buffers -- the ring, then the output row.
 template <typename T, int THREADS, int K, bool PREG, bool RMS>
-__global__ void __launch_bounds__(THREADS) norm_fwd_row_kernel(const FwdParams p) {
+__global__ void __launch_bounds__(THREADS, THREADS <= 256 ? 2 : 1) norm_fwd_row_kernel(const FwdParams p) {
   constexpr int WARPS = THREADS / 32;
   constexpr int ES = static_cast<int>(sizeof(T));
   extern __shared__ __align__(128) unsigned char dyn_smem[];
@@ -177,12 +177,16 @@ __global__ void __launch_bounds__(THREADS) norm_fwd_row_kernel(const FwdParams p
     mbar_wait(&full_bar[slot], parity, &cta_abort, p.status);
     const T* xs = reinterpret_cast<const T*>(dyn_smem + (size_t)slot * buf +
                                              (reinterpret_cast<uintptr_t>(xb + row * p.x_stride) & 15u));
-    float xv[K];
+    // All loads first, then the conversions: no load waits behind another's use.
+    T xraw[K];
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       const int c = tid + k * THREADS;
-      xv[k] = c < p.N ? to_f32(xs[c]) : 0.f;
+      xraw[k] = c < p.N ? xs[c] : from_f32<T>(0.f);
     }
+    float xv[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) xv[k] = to_f32(xraw[k]);
     // The first reduction of a row is also the point after which every thread holds its elements in
     // registers (its barrier covers the whole CTA): the slot can take the row `stages` rows ahead.
     auto refill = [&]() {
@@ -248,7 +252,7 @@ __global__ void __launch_bounds__(THREADS) norm_fwd_row_kernel(const FwdParams p
 // are re-read per row, eight columns at a time, and pass 2 recomputes from the staged rows.
 // Dynamic shared memory: (2 * stages + 1) row buffers -- the ring of (x, dy) pairs, then the output row.
 template <typename T, int THREADS, int K, bool FAT, bool RMS>
-__global__ void __launch_bounds__(THREADS) norm_bwd_dx_row_kernel(const BwdParams p) {
+__global__ void __launch_bounds__(THREADS, THREADS <= 256 ? 2 : 1) norm_bwd_dx_row_kernel(const BwdParams p) {
   constexpr int WARPS = THREADS / 32;
   constexpr int NV = RMS ? 1 : 2;
   constexpr int ES = static_cast<int>(sizeof(T));
@@ -316,13 +320,20 @@ __global__ void __launch_bounds__(THREADS) norm_bwd_dx_row_kernel(const BwdParam
     for (int k0 = 0; k0 < K; k0 += CH) {
       float wc[CH];
       if (!FAT) load_param_columns<CH>(p.w, p.w_dtype, tid + k0 * THREADS, THREADS, p.N, 1.f, wc);
+      T xraw[CH], graw[CH];  // all loads of the chunk first, then their uses
+#pragma unroll
+      for (int k = 0; k < CH; ++k) {
+        const int c = tid + (k0 + k) * THREADS;
+        xraw[k] = c < p.N ? xs[c] : from_f32<T>(0.f);
+        graw[k] = c < p.N ? gs[c] : from_f32<T>(0.f);
+      }
 #pragma unroll
       for (int k = 0; k < CH; ++k) {
         const int c = tid + (k0 + k) * THREADS;
         float xh = 0.f, wdy = 0.f;
         if (c < p.N) {
-          xh = (to_f32(xs[c]) - mu) * rs;
-          wdy = (FAT ? wr[FAT ? k0 + k : 0] : wc[k]) * to_f32(gs[c]);
+          xh = (to_f32(xraw[k]) - mu) * rs;
+          wdy = (FAT ? wr[FAT ? k0 + k : 0] : wc[k]) * to_f32(graw[k]);
         }
         s[0] += xh * wdy;
         if (!RMS) s[NV - 1] += wdy;
@@ -362,6 +373,103 @@ __global__ void __launch_bounds__(THREADS) norm_bwd_dx_row_kernel(const BwdParam
     stage_row_out<T>(s_out, dxrow, p.N, tid, THREADS);
   }
   if (tid == 0 && cta_abort) linger_after_abort();
+}
+
+// ---------------------------------------------------------------------------------------
+// Short rows of any alignment (at most 32 * K elements): one WARP per row, no shared memory.
+// Lane l takes elements l, l + 32, ...: a warp's access is one contiguous run of the row, the
+// K loads of a lane are all in flight at once, and the reductions are shuffles.  A CTA of eight
+// warps works on eight rows at a time, so short rows no longer cost a whole CTA each.
+// ---------------------------------------------------------------------------------------
+constexpr int kWarpRowWarps = 8;
+
+template <typename T, int K, bool RMS>
+__global__ void __launch_bounds__(kWarpRowWarps * 32) norm_fwd_warp_row_kernel(const FwdParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * kWarpRowWarps;
+  float wr[K], br[K];
+  load_param_columns<K>(p.w, p.w_dtype, lane, 32, p.N, 1.f, wr);
+  load_param_columns<K>(RMS ? nullptr : p.b, p.w_dtype, lane, 32, p.N, 0.f, br);
+  const float inv_n = 1.f / static_cast<float>(p.N);
+  for (int64_t row = (int64_t)blockIdx.x * kWarpRowWarps + (threadIdx.x >> 5); row < p.M; row += warps) {
+    const T* xrow = static_cast<const T*>(p.x) + row * p.x_stride;
+    T* yrow = static_cast<T*>(p.y) + row * p.y_stride;
+    T xraw[K];  // all loads first, then the conversions
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int c = lane + 32 * k;
+      xraw[k] = c < p.N ? xrow[c] : from_f32<T>(0.f);
+    }
+    float xv[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) xv[k] = to_f32(xraw[k]);
+    float mean = 0.f;
+    if (!RMS) {
+      float s = 0.f;
+#pragma unroll
+      for (int k = 0; k < K; ++k) s += xv[k];
+      mean = warp_sum(s) * inv_n;
+    }
+    float q = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const float d = (lane + 32 * k) < p.N ? xv[k] - mean : 0.f;
+      q += d * d;
+    }
+    const float rstd = 1.f / sqrtf(warp_sum(q) * inv_n + p.eps);
+    if (lane == 0) {
+      if (!RMS) p.mean[row] = mean;
+      p.rstd[row] = rstd;
+    }
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int c = lane + 32 * k;
+      if (c < p.N) yrow[c] = from_f32<T>((xv[k] - mean) * rstd * wr[k] + br[k]);
+    }
+  }
+}
+
+template <typename T, int K, bool RMS>
+__global__ void __launch_bounds__(kWarpRowWarps * 32) norm_bwd_dx_warp_row_kernel(const BwdParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * kWarpRowWarps;
+  float wr[K];
+  load_param_columns<K>(p.w, p.w_dtype, lane, 32, p.N, 1.f, wr);
+  const float inv_n = 1.f / static_cast<float>(p.N);
+  for (int64_t row = (int64_t)blockIdx.x * kWarpRowWarps + (threadIdx.x >> 5); row < p.M; row += warps) {
+    const T* xrow = static_cast<const T*>(p.x) + row * p.x_stride;
+    const T* grow = static_cast<const T*>(p.dy) + row * p.dy_stride;
+    T* dxrow = static_cast<T*>(p.dx) + row * p.dx_stride;
+    const float mu = RMS ? 0.f : __ldg(p.mean + row);
+    const float rs = __ldg(p.rstd + row);
+    T xraw[K], graw[K];  // all loads first, then their uses
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int c = lane + 32 * k;
+      xraw[k] = c < p.N ? xrow[c] : from_f32<T>(0.f);
+      graw[k] = c < p.N ? grow[c] : from_f32<T>(0.f);
+    }
+    // x and dy stay as loaded; xhat and w*dy are formed twice (three flops) instead of being kept, which
+    // leaves the registers for having every load of the row in flight at once.
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const bool live = (lane + 32 * k) < p.N;
+      const float xh = live ? (to_f32(xraw[k]) - mu) * rs : 0.f;
+      const float wdy = live ? wr[k] * to_f32(graw[k]) : 0.f;
+      s0 += xh * wdy;
+      if (!RMS) s1 += wdy;
+    }
+    const float c1 = warp_sum(s0) * inv_n;
+    const float c2 = RMS ? 0.f : warp_sum(s1) * inv_n;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int c = lane + 32 * k;
+      const float xh = (to_f32(xraw[k]) - mu) * rs;
+      const float wdy = wr[k] * to_f32(graw[k]);
+      if (c < p.N) dxrow[c] = from_f32<T>((wdy - (xh * c1 + c2)) * rs);
+    }
+  }
 }
 
 }  // namespace b200norm

@@ -19,6 +19,15 @@ struct PacketKernel {
   int threads() const { return 32 * warps_m * warps_n; }
 };
 
+// Launch shapes of the any-alignment row kernels: the first whose threads * columns-per-thread
+// covers the row is used.
+struct RowShape {
+  int threads, columns;
+};
+constexpr int kWarpRowSizes[3] = {256, 512, 1024};  // 32 lanes x 8 / 16 / 32 elements
+constexpr int kRowShapeCount = 6;
+constexpr RowShape kRowShapes[kRowShapeCount] = {{256, 4}, {256, 8}, {256, 16}, {256, 24}, {256, 32}, {1024, 32}};
+
 struct DTypeKernels {
   int elem_size;
   // [0] LayerNorm, [1] RMSNorm; each table in ascending capacity
@@ -28,19 +37,15 @@ struct DTypeKernels {
   int n_bwd[2];
   // any-alignment norm kernels (tables without a fused activation only): rows staged through shared
   // memory, [op][shape] with the shapes of kRowShapes below; dweight / dbias by a column kernel
-  const void* fwd_rows[2][4];
-  const void* bwd_dx_rows[2][4];
+  const void* fwd_rows[2][kRowShapeCount];
+  const void* bwd_dx_rows[2][kRowShapeCount];
+  // the same for short rows, one warp per row: [op][i] for rows of up to kWarpRowSizes[i] elements
+  const void* fwd_warp_rows[2][3];
+  const void* bwd_dx_warp_rows[2][3];
   const void* bwd_dwdb_any[2];
   const void* act_packet[2];    // stand-alone activation, [0] forward [1] backward (tables of an activation only)
   const void* act_any[2];
 };
-
-// Launch shapes of the any-alignment row kernels: the first whose threads * columns-per-thread
-// covers the row is used.
-struct RowShape {
-  int threads, columns;
-};
-constexpr RowShape kRowShapes[4] = {{256, 4}, {256, 16}, {256, 32}, {1024, 32}};
 
 // Softmax / LogSoftmax: one shape list per storage type; fn[log][bwd].
 struct SoftmaxKernel {
