@@ -237,7 +237,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
           const float2* b2 = reinterpret_cast<const float2*>(&b_s[v * VEC]);
 #pragma unroll
           for (int h = 0; h < H; ++h) {
-            const float2 y = fma2(mul2(add2(xf[h], nmu2), rs2), w2[h], b2[h]);
+            const float2 y = fma2(mul2(RMS ? xf[h] : add2(xf[h], nmu2), rs2), w2[h], b2[h]);
             gf[h] = mul2(gf[h], act_grad2<ACT>(y));
           }
           if (!KEEP) {
@@ -247,7 +247,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
         }
 #pragma unroll
         for (int h = 0; h < H; ++h) {
-          const float2 xh = mul2(add2(xf[h], nmu2), rs2);
+          const float2 xh = mul2(RMS ? xf[h] : add2(xf[h], nmu2), rs2);  // RMSNorm: mean is zero
           const float2 wdy = mul2(w2[h], gf[h]);
           dw[j][h] = fma2(gf[h], xh, dw[j][h]);
           if (!RMS) db[j][h] = add2(db[j][h], gf[h]);

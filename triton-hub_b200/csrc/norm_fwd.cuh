@@ -280,7 +280,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
       float2 yf[H];
       if (PREG) {
 #pragma unroll
-        for (int h = 0; h < H; ++h) yf[h] = fma2(mul2(add2(xf[j][h], nm), r2), wr[j][h], br[j][h]);
+        for (int h = 0; h < H; ++h) yf[h] = fma2(mul2(RMS ? xf[j][h] : add2(xf[j][h], nm), r2), wr[j][h], br[j][h]);
       } else if (v < Vl) {
         float wf[VEC], bf[VEC];
 #pragma unroll
@@ -292,7 +292,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
         if (!RMS && p.b != nullptr) load_param_packet<T>(p.b, p.w_dtype, v0 + v, bf);
 #pragma unroll
         for (int h = 0; h < H; ++h)
-          yf[h] = fma2(mul2(add2(xf[j][h], nm), r2), make_float2(wf[2 * h], wf[2 * h + 1]),
+          yf[h] = fma2(mul2(RMS ? xf[j][h] : add2(xf[j][h], nm), r2), make_float2(wf[2 * h], wf[2 * h + 1]),
                        make_float2(bf[2 * h], bf[2 * h + 1]));
       }
       if (ACT != kActNone && v < Vl) {

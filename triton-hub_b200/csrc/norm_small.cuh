@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(kSmallWarps * 32) norm_fwd_small_kernel(const 
       float2 yf[H];
 #pragma unroll
       for (int h = 0; h < H; ++h) {
-        yf[h] = fma2(mul2(add2(xf[j][h], nm), r2), wr[j][h], br[j][h]);
+        yf[h] = fma2(mul2(RMS ? xf[j][h] : add2(xf[j][h], nm), r2), wr[j][h], br[j][h]);
         if (ACT != kActNone) yf[h] = act_fwd2<ACT>(yf[h]);
       }
       if (valid && v < p.V) st_stream(yrow + v, Pack16<T>::pack2(yf));
@@ -174,14 +174,14 @@ __global__ void __launch_bounds__(kSmallWarps * 32) norm_bwd_small_kernel(const 
       if (ACT != kActNone) {  // dy = dz * act'(y), rounded to the storage type like a separate kernel would
 #pragma unroll
         for (int h = 0; h < H; ++h) {
-          const float2 y = fma2(mul2(add2(xf[h], nmu2), rs2), wr[j][h], br[j < BL ? j : 0][h]);
+          const float2 y = fma2(mul2(RMS ? xf[h] : add2(xf[h], nmu2), rs2), wr[j][h], br[j < BL ? j : 0][h]);
           gf[h] = mul2(gf[h], act_grad2<ACT>(y));
         }
         Pack16<T>::unpack2(Pack16<T>::pack2(gf), gf);
       }
 #pragma unroll
       for (int h = 0; h < H; ++h) {  // masked packets and rows carry dy = 0: they add nothing
-        xh[j][h] = mul2(add2(xf[h], nmu2), rs2);
+        xh[j][h] = mul2(RMS ? xf[h] : add2(xf[h], nmu2), rs2);
         wdy[j][h] = mul2(wr[j][h], gf[h]);
         dw[j][h] = fma2(gf[h], xh[j][h], dw[j][h]);
         if (!RMS) db[j][h] = add2(db[j][h], gf[h]);
