@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
   constexpr int TPR = WARPS_N * 32;
   constexpr int NV = RMS ? 1 : 2;
   constexpr int NBAR = STAGES > 0 ? WARPS_M * STAGES : 1;
-  __shared__ float pair_sums[2][NV];  // CL == 2: the partner's row sums, double-buffered
+  __shared__ __align__(8) PairBox<NV> pair_box[2];  // CL == 2: the partner's row sums, double-buffered
   // w as fp32 (N), later the (WARPS_M, N) sums; then, 128-byte aligned, the row slots
   extern __shared__ __align__(128) unsigned char dyn_smem[];
   __shared__ float red_smem[WARPS_M][2 * NV * WARPS_N];
@@ -90,6 +90,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
   const int v0 = static_cast<int>(cr) * Vl;      // ... starting at this one
   const int Nl = Vl * VEC;                       // the same in elements
   int pair_buf = 0;
+  uint32_t pair_seq = 0;  // exchanges with the partner so far
   const int shard = unit / p.ctas_per_shard;
   const int cta_in_shard = unit - shard * p.ctas_per_shard;
   const int64_t row_begin = (int64_t)shard * p.rows_per_shard;
@@ -153,8 +154,12 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
 #pragma unroll
         for (int e = 0; e < VEC; ++e) dst[e] = f[e];
       });
+  if (CL > 1 && threadIdx.x == 0) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) pair_box[0].w[i] = pair_box[1].w[i] = 0ull;
+  }
   __syncthreads();
-  if (CL > 1) cluster_sync_all();  // the partner CTA is running: its shared memory may be written
+  if (CL > 1) cluster_sync_all();  // the partner CTA is running and both boxes are clear: its shared memory may be written
 
   // Per-element values live as fp32 pairs (two per instruction, norm_common.cuh): H pairs per packet.
   constexpr int H = VEC / 2;
@@ -268,17 +273,10 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
     group_sum<WARPS_N, NV, (WARPS_M == 1 ? 0 : 1)>(s, red_smem[warp_m], phase, warp_m, warp_n, lane);
     if (CL > 1) {
       // Swap this half's sums with the partner's and add them in rank order.
-      if (threadIdx.x == 0) {
+      float other[NV];
+      pair_swap<NV>(s, other, pair_box, pair_buf, ++pair_seq, cr, &cta_abort, p.status);
 #pragma unroll
-        for (int i = 0; i < NV; ++i) st_cluster_f32(cluster_map(smem_addr(&pair_sums[pair_buf][i]), cr ^ 1u), s[i]);
-      }
-      cluster_sync_all();
-#pragma unroll
-      for (int i = 0; i < NV; ++i) {
-        const float other = pair_sums[pair_buf][i];
-        s[i] = (cr == 0) ? s[i] + other : other + s[i];
-      }
-      pair_buf ^= 1;
+      for (int i = 0; i < NV; ++i) s[i] = (cr == 0) ? s[i] + other[i] : other[i] + s[i];
     }
     if (STAGES > 0) {
       // Every thread of the group holds its packets in registers: the slot can be refilled.
@@ -341,6 +339,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_bwd_kernel(c
     if (t == 0 && cta_abort) drain_ring<STAGES>(bars, first < row_end ? (row_end - first + step - 1) / step : 0);
   }
 
+  if (CL > 1) cluster_sync_all();  // neither CTA of a pair leaves while the other may still store into it
   // One partial row per unit: add the row groups in order, then row group 0 stores.
   if (WARPS_M > 1) {
     float* acc = reinterpret_cast<float*>(dyn_smem);  // (WARPS_M, N); the weights are no longer needed

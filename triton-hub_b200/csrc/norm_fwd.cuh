@@ -55,15 +55,16 @@ struct FwdParams {
 // normalised tensor never goes to memory on its own.
 template <typename T, int LDGS, int WARPS_M, int WARPS_N, bool PREG, int STAGES, int MINB, int CL, int ACT, bool RMS>
 __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(const FwdParams p) {
-  static_assert(CL == 1 || (CL == 2 && WARPS_M == 1), "cluster split: one row group per CTA");
+  static_assert(CL == 1 || (CL == 2 && WARPS_M == 1 && STAGES > 0), "cluster split: one row group per CTA, staged rows");
   constexpr int VEC = Pack16<T>::kElems;
-  __shared__ float pair_box[2][2];  // CL == 2: the partner's statistics, double-buffered
+  __shared__ __align__(8) PairBox<2> pair_box[2];  // CL == 2: the partner's statistics, double-buffered
   const uint32_t cr = (CL > 1) ? cluster_cta_rank() : 0u;
   const int unit = (CL > 1) ? static_cast<int>(blockIdx.x) / CL : static_cast<int>(blockIdx.x);
   const int units = static_cast<int>(gridDim.x) / CL;
   const int Vl = p.V / CL;                   // packets of each row this CTA handles ...
   const int v0 = static_cast<int>(cr) * Vl;  // ... starting at this one
   int pair_buf = 0;
+  uint32_t pair_seq = 0;  // exchanges with the partner so far
   constexpr int TPR = WARPS_N * 32;  // threads per row
   constexpr int NBAR = STAGES > 0 ? WARPS_M * STAGES : 1;
   extern __shared__ __align__(128) unsigned char dyn_smem[];  // (WARPS_M, STAGES, row bytes)
@@ -94,7 +95,13 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
   }
   grid_dependency_sync();  // nothing above reads global memory
   trigger_dependents();
-  if (CL > 1) cluster_sync_all();  // the partner CTA is running: its shared memory may be written
+  if (CL > 1) {
+    if (threadIdx.x == 0) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) pair_box[0].w[i] = pair_box[1].w[i] = 0ull;
+    }
+    cluster_sync_all();  // the partner CTA is running and both boxes are clear: its shared memory may be written
+  }
   auto first_fills = [&]() {  // the group leader requests the first STAGES rows
     if (STAGES > 0 && t == 0) {
 #pragma unroll
@@ -197,7 +204,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
         if (CL > 1) {  // merge the two halves (equal counts), rank 0's first
           const float mine[2] = {mean, q[0]};
           float theirs[2];
-          pair_swap<2>(mine, theirs, pair_box, pair_buf, cr);
+          pair_swap<2>(mine, theirs, pair_box, pair_buf, ++pair_seq, cr, &cta_abort, p.status);
           const float m0 = cr == 0 ? mine[0] : theirs[0], m1 = cr == 0 ? theirs[0] : mine[0];
           const float q0 = cr == 0 ? mine[1] : theirs[1], q1 = cr == 0 ? theirs[1] : mine[1];
           const float d = m1 - m0;
@@ -211,7 +218,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
         if (CL > 1) {
           const float mine[2] = {s[0], 0.f};
           float theirs[2];
-          pair_swap<2>(mine, theirs, pair_box, pair_buf, cr);
+          pair_swap<2>(mine, theirs, pair_box, pair_buf, ++pair_seq, cr, &cta_abort, p.status);
           s[0] = cr == 0 ? mine[0] + theirs[0] : theirs[0] + mine[0];
         }
         mean = s[0] * inv_n;
@@ -226,7 +233,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
       if (CL > 1) {
         const float mine[2] = {q[0], 0.f};
         float theirs[2];
-        pair_swap<2>(mine, theirs, pair_box, pair_buf, cr);
+        pair_swap<2>(mine, theirs, pair_box, pair_buf, ++pair_seq, cr, &cta_abort, p.status);
         q[0] = cr == 0 ? mine[0] + theirs[0] : theirs[0] + mine[0];
       }
     }
@@ -261,7 +268,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
       if (CL > 1) {
         const float mine[2] = {q[0], 0.f};
         float theirs[2];
-        pair_swap<2>(mine, theirs, pair_box, pair_buf, cr);
+        pair_swap<2>(mine, theirs, pair_box, pair_buf, ++pair_seq, cr, &cta_abort, p.status);
         q[0] = cr == 0 ? mine[0] + theirs[0] : theirs[0] + mine[0];
       }
     }
@@ -305,6 +312,7 @@ __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MINB) norm_fwd_kernel(c
   if (STAGES > 0) {
     if (t == 0 && cta_abort) drain_ring<STAGES>(bars, first < p.M ? (p.M - first + step - 1) / step : 0);
   }
+  if (CL > 1) cluster_sync_all();  // neither CTA of a pair leaves while the other may still store into it
 }
 
 }  // namespace b200norm

@@ -113,21 +113,68 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-// Swap NV floats with the partner CTA of a pair: `mine` goes into the partner's `box`, the
-// cluster barrier orders the two remote stores, and the partner's values are read from this
-// CTA's own `box`.  `box` is double-buffered by the caller (`buf` flips per call), so a CTA that
-// races ahead cannot overwrite values its partner has not read yet: a full cluster barrier lies
-// between two uses of the same buffer.
+// Exchange of NV floats with the partner CTA of a pair, point to point and without any fence.
+// Thread 0 stores each value together with the exchange's sequence number as ONE 8-byte word into
+// the partner's `box`; every thread polls its own CTA's box until the words carry that number.  A
+// word is never torn, so a matching number vouches for its value and nothing has to be ordered.
+// That matters: a cluster barrier (or any release / acquire at cluster scope) makes the warp wait
+// until its earlier GLOBAL stores -- the previous row's output -- are acknowledged, once per row
+// (`membar` was the top stall of the pair kernels: 3.2 per issued instruction, 0.77-0.86 of the copy
+// bandwidth whatever the launch shape).  The wait is bounded like mbar_wait.  `box` is
+// double-buffered by the caller (`buf` flips per call): the partner can be at most one exchange
+// ahead, because its next-but-one exchange needs this CTA's answer to its next, which thread 0
+// sends only after every thread of this CTA has read the current values (a CTA-wide barrier -- the
+// next row's reduction -- lies in between).
 template <int NV>
-__device__ __forceinline__ void pair_swap(const float (&mine)[NV], float (&theirs)[NV], float (*box)[NV], int& buf,
-                                          uint32_t cr) {
+struct PairBox {
+  unsigned long long w[NV];  // {fp32 value (low word), sequence number (high word)}
+};
+
+__device__ __forceinline__ void st_cluster_u64(uint32_t addr, unsigned long long v) {
+  asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(addr), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_volatile_shared_u64(const void* p) {
+  unsigned long long v;
+  asm volatile("ld.volatile.shared.u64 %0, [%1];" : "=l"(v) : "r"(smem_addr(p)) : "memory");
+  return v;
+}
+
+template <int NV>
+__device__ __forceinline__ void pair_swap(const float (&mine)[NV], float (&theirs)[NV], PairBox<NV>* box, int& buf,
+                                          uint32_t seq, uint32_t cr, volatile int* cta_abort, int* status) {
+  PairBox<NV>* b = box + buf;
   if (threadIdx.x == 0) {
 #pragma unroll
-    for (int i = 0; i < NV; ++i) st_cluster_f32(cluster_map(smem_addr(&box[buf][i]), cr ^ 1u), mine[i]);
+    for (int i = 0; i < NV; ++i)
+      st_cluster_u64(cluster_map(smem_addr(&b->w[i]), cr ^ 1u),
+                     (static_cast<unsigned long long>(seq) << 32) | __float_as_uint(mine[i]));
   }
-  cluster_sync_all();
+  unsigned long long got[NV];
+  auto arrived = [&]() {
+    bool ok = true;
 #pragma unroll
-  for (int i = 0; i < NV; ++i) theirs[i] = box[buf][i];
+    for (int i = 0; i < NV; ++i) {
+      got[i] = ld_volatile_shared_u64(&b->w[i]);
+      ok = ok && static_cast<uint32_t>(got[i] >> 32) == seq;
+    }
+    return ok;
+  };
+  if (!arrived() && !*cta_abort) {
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+      bool ok = false;
+#pragma unroll 1
+      for (int i = 0; i < 256 && !ok; ++i) ok = arrived();
+      if (ok || *cta_abort) break;
+      if (global_ns() - t0 > kWaitLimitNs) {
+        *cta_abort = 1;
+        if (status != nullptr) *reinterpret_cast<volatile int*>(status) = 4;  // B200NORM_ERR_TIMEOUT
+        break;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i) theirs[i] = __uint_as_float(static_cast<uint32_t>(got[i]));
   buf ^= 1;
 }
 
