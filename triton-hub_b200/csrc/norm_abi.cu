@@ -173,13 +173,6 @@ bool aligned16(const void* p, int64_t stride_elems, int es) {
   return (reinterpret_cast<uintptr_t>(p) & 15u) == 0 && ((stride_elems * es) & 15) == 0;
 }
 
-// Shape of the any-alignment row kernels for a row of N elements (norm_table.h).
-int row_shape(int64_t N) {
-  for (int i = 0; i < kRowShapeCount; ++i)
-    if ((int64_t)kRowShapes[i].threads * kRowShapes[i].columns >= N) return i;
-  return kRowShapeCount - 1;  // unreachable: 1024 x 32 covers the 64 KB row limit for every storage type
-}
-
 // Dynamic shared memory of a backward launch, per CTA: (warps_m [+1 with a fused activation: the
 // bias]) x columns fp32 for the weights and the row-group sums, padded to 128 bytes, then the
 // x + dy row slots.  A CTA of a pair holds half of the columns.
@@ -255,9 +248,9 @@ int launch_row_kernel(DeviceState& dev, const void* const (&fns)[kRowShapeCount]
     const int grid = static_cast<int>(std::min<int64_t>(want, (int64_t)dev.sm_count * occ));
     return launch(fn, dim3(grid), dim3(kWarpRowWarps * 32), 0, params, stream, false);
   }
-  const int shape = row_shape(N);
+  const int shape = N <= kRowSplit ? 0 : 1;
   const void* fn = fns[shape];
-  const int threads = kRowShapes[shape].threads;
+  const int threads = kRowThreads[shape];
   const size_t buf = row_buffer_bytes(N, es);
   auto bytes = [&](int slots) { return (static_cast<size_t>(rows_per_slot) * slots + 1) * buf; };
   int slots = 4;

@@ -9,10 +9,11 @@
 //                      by one; the row lands at the same offset within a 16-byte line as in global
 //                      memory, so element i sits at a fixed place whatever the row's alignment.
 //                      A ring of up to four such slots per CTA keeps that many rows in flight;
-//   shared -> regs   : thread t takes elements t, t + THREADS, ... (K of them) -- one trip to
-//                      global memory per row, the passes after that run on registers;
-//   regs -> shared -> global : the result row is laid out at ITS alignment and written back with
-//                      128-bit stores for the interior.
+//   shared -> shared : every pass (sum, centred squares, output) streams the row out of shared
+//                      memory, thread t taking elements t, t + THREADS, ...: one trip to global
+//                      memory per row, no element kept in a register across a reduction;
+//   shared -> global : the result row is laid out at ITS alignment and written back with 128-bit
+//                      stores for the interior.
 //
 // One CTA works on one row at a time and walks the rows grid-strided.  Forward: statistics by the
 // reference's two passes (mean, then centred squares).  Backward: dx here, dweight / dbias by the
@@ -121,11 +122,31 @@ __host__ __device__ inline size_t row_buffer_bytes(int64_t N, int es) {
   return (static_cast<size_t>(N) * es + 16 + 15) & ~static_cast<size_t>(15);
 }
 
-// Forward.  THREADS * K >= N.  PREG: weight and bias sit in registers for the life of the CTA;
-// without it (1024 threads leave 64 registers each) they are re-read per row, eight columns at a time.
+// One parameter element of storage type P as fp32.
+template <typename P>
+__device__ __forceinline__ float param_at(const void* p, int c) {
+  return to_f32(__ldg(static_cast<const P*>(p) + c));
+}
+
+// Calls body(tag) with a value of the parameter vectors' storage type, switched on ONCE outside the
+// element loops.
+template <typename Body>
+__device__ __forceinline__ void with_param_type(int dtype, Body body) {
+  switch (dtype) {
+    case kF32: body(float{}); break;
+    case kF16: body(__half{}); break;
+    case kBF16: body(__nv_bfloat16{}); break;
+    default: body(double{}); break;
+  }
+}
+
+// Forward.  The staged row is streamed out of shared memory once per pass (sum, centred squares,
+// output): no element lives in a register across a reduction, so one kernel shape serves every row
+// length, nothing is predicated off for short rows and the register count stays low enough for
+// several CTAs per SM.  Weight and bias are read through L1 as the output is formed.
 // Dynamic shared memory: (stages + 1) row buffers -- the ring, then the output row.
-template <typename T, int THREADS, int K, bool PREG, bool RMS>
-__global__ void __launch_bounds__(THREADS, THREADS <= 256 ? 2 : 1) norm_fwd_row_kernel(const FwdParams p) {
+template <typename T, int THREADS, bool RMS>
+__global__ void __launch_bounds__(THREADS) norm_fwd_row_kernel(const FwdParams p) {
   constexpr int WARPS = THREADS / 32;
   constexpr int ES = static_cast<int>(sizeof(T));
   extern __shared__ __align__(128) unsigned char dyn_smem[];
@@ -138,17 +159,18 @@ __global__ void __launch_bounds__(THREADS, THREADS <= 256 ? 2 : 1) norm_fwd_row_
   unsigned char* s_out = dyn_smem + (size_t)stages * buf;
   int phase_bit = 0;
   const T* xb = static_cast<const T*>(p.x);
+  const int N = p.N;
 
   auto fill = [&](int slot, int64_t row) {  // every thread calls it; the leader arms the barrier and copies
     const T* xrow = xb + row * p.x_stride;
-    const RowSpan<T> sp(xrow, p.N);
+    const RowSpan<T> sp(xrow, N);
     unsigned char* shm = dyn_smem + (size_t)slot * buf;
     if (tid == 0) {
       mbar_expect_tx(&full_bar[slot], static_cast<uint32_t>(sp.body_bytes));
       if (sp.body_bytes > 0)
         bulk_load(shm + sp.phase + sp.head * ES, xrow + sp.head, static_cast<uint32_t>(sp.body_bytes), &full_bar[slot]);
     }
-    copy_row_edges<T>(shm, xrow, p.N, sp, tid, THREADS);
+    copy_row_edges<T>(shm, xrow, N, sp, tid, THREADS);
   };
 
   if (tid == 0) {
@@ -157,19 +179,12 @@ __global__ void __launch_bounds__(THREADS, THREADS <= 256 ? 2 : 1) norm_fwd_row_
     mbar_init_fence();
   }
   __syncthreads();
-  constexpr int PK = PREG ? K : 1;
-  constexpr int CH = K < 8 ? K : 8;  // columns per parameter chunk without PREG
-  float wr[PK], br[PK];
-  if (PREG) {
-    load_param_columns<PK>(p.w, p.w_dtype, tid, THREADS, p.N, 1.f, wr);
-    load_param_columns<PK>(RMS ? nullptr : p.b, p.w_dtype, tid, THREADS, p.N, 0.f, br);
-  }
   for (int s = 0; s < stages; ++s) {
     const int64_t r = (int64_t)blockIdx.x + (int64_t)s * gridDim.x;
     if (r < p.M) fill(s, r);
   }
   __syncthreads();  // the edge elements of the first rows are in place
-  const float inv_n = 1.f / static_cast<float>(p.N);
+  const float inv_n = 1.f / static_cast<float>(N);
   int slot = 0;
   uint32_t parity = 0;
   for (int64_t row = blockIdx.x; row < p.M; row += gridDim.x) {
@@ -177,82 +192,64 @@ __global__ void __launch_bounds__(THREADS, THREADS <= 256 ? 2 : 1) norm_fwd_row_
     mbar_wait(&full_bar[slot], parity, &cta_abort, p.status);
     const T* xs = reinterpret_cast<const T*>(dyn_smem + (size_t)slot * buf +
                                              (reinterpret_cast<uintptr_t>(xb + row * p.x_stride) & 15u));
-    // All loads first, then the conversions: no load waits behind another's use.
-    T xraw[K];
-#pragma unroll
-    for (int k = 0; k < K; ++k) {
-      const int c = tid + k * THREADS;
-      xraw[k] = c < p.N ? xs[c] : from_f32<T>(0.f);
+    float mean = 0.f;
+    if (!RMS) {
+      float s[1] = {0.f};
+#pragma unroll 4
+      for (int c = tid; c < N; c += THREADS) s[0] += to_f32(xs[c]);
+      group_sum<WARPS, 1, 0>(s, red, phase_bit, 0, warp, lane);
+      mean = s[0] * inv_n;
     }
-    float xv[K];
-#pragma unroll
-    for (int k = 0; k < K; ++k) xv[k] = to_f32(xraw[k]);
-    // The first reduction of a row is also the point after which every thread holds its elements in
-    // registers (its barrier covers the whole CTA): the slot can take the row `stages` rows ahead.
-    auto refill = [&]() {
+    float q[1] = {0.f};
+#pragma unroll 4
+    for (int c = tid; c < N; c += THREADS) {
+      const float d = to_f32(xs[c]) - mean;
+      q[0] += d * d;
+    }
+    group_sum<WARPS, 1, 0>(q, red, phase_bit, 0, warp, lane);
+    const float rstd = 1.f / sqrtf(q[0] * inv_n + p.eps);
+    if (tid == 0) {
+      if (!RMS) p.mean[row] = mean;
+      p.rstd[row] = rstd;
+    }
+    // s_out is free: every thread passed the reductions above after its part of the previous copy-out
+    T* ys = reinterpret_cast<T*>(s_out + static_cast<int>(reinterpret_cast<uintptr_t>(yrow) & 15u));
+    with_param_type(p.w_dtype, [&](auto tag) {
+      using P = decltype(tag);
+      if (p.w != nullptr && !RMS && p.b != nullptr) {
+#pragma unroll 4
+        for (int c = tid; c < N; c += THREADS)
+          ys[c] = from_f32<T>((to_f32(xs[c]) - mean) * rstd * param_at<P>(p.w, c) + param_at<P>(p.b, c));
+      } else if (p.w != nullptr) {
+#pragma unroll 4
+        for (int c = tid; c < N; c += THREADS) ys[c] = from_f32<T>((to_f32(xs[c]) - mean) * rstd * param_at<P>(p.w, c));
+      } else if (!RMS && p.b != nullptr) {
+#pragma unroll 4
+        for (int c = tid; c < N; c += THREADS) ys[c] = from_f32<T>((to_f32(xs[c]) - mean) * rstd + param_at<P>(p.b, c));
+      } else {
+#pragma unroll 4
+        for (int c = tid; c < N; c += THREADS) ys[c] = from_f32<T>((to_f32(xs[c]) - mean) * rstd);
+      }
+    });
+    __syncthreads();  // the output row is complete, and every thread is done reading the slot
+    {
       const int64_t r = row + (int64_t)stages * gridDim.x;
       if (r < p.M) fill(slot, r);
       if (++slot == stages) {
         slot = 0;
         parity ^= 1u;
       }
-    };
-    float mean = 0.f;
-    if (!RMS) {
-      float s[1] = {0.f};
-#pragma unroll
-      for (int k = 0; k < K; ++k) s[0] += xv[k];
-      group_sum<WARPS, 1, 0>(s, red, phase_bit, 0, warp, lane);
-      refill();
-      mean = s[0] * inv_n;
     }
-    float q[1] = {0.f};
-#pragma unroll
-    for (int k = 0; k < K; ++k) {
-      const float d = (tid + k * THREADS) < p.N ? xv[k] - mean : 0.f;
-      q[0] += d * d;
-    }
-    group_sum<WARPS, 1, 0>(q, red, phase_bit, 0, warp, lane);
-    if (RMS) refill();
-    const float rstd = 1.f / sqrtf(q[0] * inv_n + p.eps);
-    if (tid == 0) {
-      if (!RMS) p.mean[row] = mean;
-      p.rstd[row] = rstd;
-    }
-    T* ys = reinterpret_cast<T*>(s_out + static_cast<int>(reinterpret_cast<uintptr_t>(yrow) & 15u));
-    if (PREG) {
-#pragma unroll
-      for (int k = 0; k < K; ++k) {
-        const int c = tid + k * THREADS;
-        if (c < p.N) ys[c] = from_f32<T>((xv[k] - mean) * rstd * wr[PREG ? k : 0] + br[PREG ? k : 0]);
-      }
-    } else {
-#pragma unroll
-      for (int k0 = 0; k0 < K; k0 += CH) {
-        float wc[CH], bc[CH];
-        load_param_columns<CH>(p.w, p.w_dtype, tid + k0 * THREADS, THREADS, p.N, 1.f, wc);
-        load_param_columns<CH>(RMS ? nullptr : p.b, p.w_dtype, tid + k0 * THREADS, THREADS, p.N, 0.f, bc);
-#pragma unroll
-        for (int k = 0; k < CH; ++k) {
-          const int c = tid + (k0 + k) * THREADS;
-          if (c < p.N) ys[c] = from_f32<T>((xv[k0 + k] - mean) * rstd * wc[k] + bc[k]);
-        }
-      }
-    }
-    __syncthreads();
-    stage_row_out<T>(s_out, yrow, p.N, tid, THREADS);
-    // s_out is written again only after the next row's first reduction, whose barrier every thread
-    // reaches after its part of this copy-out.
+    stage_row_out<T>(s_out, yrow, N, tid, THREADS);
   }
   if (tid == 0 && cta_abort) linger_after_abort();
 }
 
-// Backward, dx only.  THREADS * K >= N.  FAT (256 threads): the weights sit in registers and xhat and
-// w*dy stay there between the two passes; otherwise (1024 threads, 64 registers each) the weights
-// are re-read per row, eight columns at a time, and pass 2 recomputes from the staged rows.
-// Dynamic shared memory: (2 * stages + 1) row buffers -- the ring of (x, dy) pairs, then the output row.
-template <typename T, int THREADS, int K, bool FAT, bool RMS>
-__global__ void __launch_bounds__(THREADS, THREADS <= 256 ? 2 : 1) norm_bwd_dx_row_kernel(const BwdParams p) {
+// Backward, dx only, streamed out of shared memory the same way (two passes over the staged x and dy
+// rows).  Dynamic shared memory: (2 * stages + 1) row buffers -- the ring of (x, dy) pairs, then the
+// output row.
+template <typename T, int THREADS, bool RMS>
+__global__ void __launch_bounds__(THREADS) norm_bwd_dx_row_kernel(const BwdParams p) {
   constexpr int WARPS = THREADS / 32;
   constexpr int NV = RMS ? 1 : 2;
   constexpr int ES = static_cast<int>(sizeof(T));
@@ -267,11 +264,12 @@ __global__ void __launch_bounds__(THREADS, THREADS <= 256 ? 2 : 1) norm_bwd_dx_r
   int phase_bit = 0;
   const T* xb = static_cast<const T*>(p.x);
   const T* gb = static_cast<const T*>(p.dy);
+  const int N = p.N;
 
   auto fill = [&](int slot, int64_t row) {
     const T* xrow = xb + row * p.x_stride;
     const T* grow = gb + row * p.dy_stride;
-    const RowSpan<T> sx(xrow, p.N), sg(grow, p.N);
+    const RowSpan<T> sx(xrow, N), sg(grow, N);
     unsigned char* shx = dyn_smem + (size_t)(2 * slot) * buf;
     unsigned char* shg = shx + buf;
     if (tid == 0) {
@@ -281,8 +279,8 @@ __global__ void __launch_bounds__(THREADS, THREADS <= 256 ? 2 : 1) norm_bwd_dx_r
       if (sg.body_bytes > 0)
         bulk_load(shg + sg.phase + sg.head * ES, grow + sg.head, static_cast<uint32_t>(sg.body_bytes), &full_bar[slot]);
     }
-    copy_row_edges<T>(shx, xrow, p.N, sx, tid, THREADS);
-    copy_row_edges<T>(shg, grow, p.N, sg, tid, THREADS);
+    copy_row_edges<T>(shx, xrow, N, sx, tid, THREADS);
+    copy_row_edges<T>(shg, grow, N, sg, tid, THREADS);
   };
 
   if (tid == 0) {
@@ -291,16 +289,12 @@ __global__ void __launch_bounds__(THREADS, THREADS <= 256 ? 2 : 1) norm_bwd_dx_r
     mbar_init_fence();
   }
   __syncthreads();
-  constexpr int PK = FAT ? K : 1;
-  constexpr int CH = K < 8 ? K : 8;
-  float wr[PK];
-  if (FAT) load_param_columns<PK>(p.w, p.w_dtype, tid, THREADS, p.N, 1.f, wr);
   for (int s = 0; s < stages; ++s) {
     const int64_t r = (int64_t)blockIdx.x + (int64_t)s * gridDim.x;
     if (r < p.M) fill(s, r);
   }
   __syncthreads();
-  const float inv_n = 1.f / static_cast<float>(p.N);
+  const float inv_n = 1.f / static_cast<float>(N);
   int slot = 0;
   uint32_t parity = 0;
   for (int64_t row = blockIdx.x; row < p.M; row += gridDim.x) {
@@ -312,55 +306,31 @@ __global__ void __launch_bounds__(THREADS, THREADS <= 256 ? 2 : 1) norm_bwd_dx_r
                                              (reinterpret_cast<uintptr_t>(xb + row * p.x_stride) & 15u));
     const T* gs = reinterpret_cast<const T*>(dyn_smem + (size_t)(2 * slot + 1) * buf +
                                              (reinterpret_cast<uintptr_t>(gb + row * p.dy_stride) & 15u));
-    float xh_k[PK], wdy_k[PK];
-    float s[NV];
+    T* os = reinterpret_cast<T*>(s_out + static_cast<int>(reinterpret_cast<uintptr_t>(dxrow) & 15u));
+    with_param_type(p.w_dtype, [&](auto tag) {
+      using P = decltype(tag);
+      const bool has_w = p.w != nullptr;
+      float s[NV];
 #pragma unroll
-    for (int i = 0; i < NV; ++i) s[i] = 0.f;
-#pragma unroll
-    for (int k0 = 0; k0 < K; k0 += CH) {
-      float wc[CH];
-      if (!FAT) load_param_columns<CH>(p.w, p.w_dtype, tid + k0 * THREADS, THREADS, p.N, 1.f, wc);
-      T xraw[CH], graw[CH];  // all loads of the chunk first, then their uses
-#pragma unroll
-      for (int k = 0; k < CH; ++k) {
-        const int c = tid + (k0 + k) * THREADS;
-        xraw[k] = c < p.N ? xs[c] : from_f32<T>(0.f);
-        graw[k] = c < p.N ? gs[c] : from_f32<T>(0.f);
-      }
-#pragma unroll
-      for (int k = 0; k < CH; ++k) {
-        const int c = tid + (k0 + k) * THREADS;
-        float xh = 0.f, wdy = 0.f;
-        if (c < p.N) {
-          xh = (to_f32(xraw[k]) - mu) * rs;
-          wdy = (FAT ? wr[FAT ? k0 + k : 0] : wc[k]) * to_f32(graw[k]);
-        }
+      for (int i = 0; i < NV; ++i) s[i] = 0.f;
+#pragma unroll 4
+      for (int c = tid; c < N; c += THREADS) {
+        const float xh = (to_f32(xs[c]) - mu) * rs;
+        const float wdy = (has_w ? param_at<P>(p.w, c) : 1.f) * to_f32(gs[c]);
         s[0] += xh * wdy;
         if (!RMS) s[NV - 1] += wdy;
-        if (FAT) {
-          xh_k[FAT ? k0 + k : 0] = xh;
-          wdy_k[FAT ? k0 + k : 0] = wdy;
-        }
       }
-    }
-    group_sum<WARPS, NV, 0>(s, red, phase_bit, 0, warp, lane);
-    const float c1 = s[0] * inv_n;
-    const float c2 = RMS ? 0.f : s[NV - 1] * inv_n;
-    T* os = reinterpret_cast<T*>(s_out + static_cast<int>(reinterpret_cast<uintptr_t>(dxrow) & 15u));
-#pragma unroll
-    for (int k0 = 0; k0 < K; k0 += CH) {
-      float wc[CH];
-      if (!FAT) load_param_columns<CH>(p.w, p.w_dtype, tid + k0 * THREADS, THREADS, p.N, 1.f, wc);
-#pragma unroll
-      for (int k = 0; k < CH; ++k) {
-        const int c = tid + (k0 + k) * THREADS;
-        if (c < p.N) {
-          const float xh = FAT ? xh_k[FAT ? k0 + k : 0] : (to_f32(xs[c]) - mu) * rs;
-          const float wdy = FAT ? wdy_k[FAT ? k0 + k : 0] : wc[k] * to_f32(gs[c]);
-          os[c] = from_f32<T>((wdy - (xh * c1 + c2)) * rs);
-        }
+      group_sum<WARPS, NV, 0>(s, red, phase_bit, 0, warp, lane);
+      const float c1 = s[0] * inv_n;
+      const float c2 = RMS ? 0.f : s[NV - 1] * inv_n;
+      // s_out is free: every thread passed the reduction after its part of the previous copy-out
+#pragma unroll 4
+      for (int c = tid; c < N; c += THREADS) {
+        const float xh = (to_f32(xs[c]) - mu) * rs;
+        const float wdy = (has_w ? param_at<P>(p.w, c) : 1.f) * to_f32(gs[c]);
+        os[c] = from_f32<T>((wdy - (xh * c1 + c2)) * rs);
       }
-    }
+    });
     __syncthreads();  // the output row is complete, and every thread is done reading the slot
     {
       const int64_t r = row + (int64_t)stages * gridDim.x;
@@ -370,7 +340,7 @@ __global__ void __launch_bounds__(THREADS, THREADS <= 256 ? 2 : 1) norm_bwd_dx_r
         parity ^= 1u;
       }
     }
-    stage_row_out<T>(s_out, dxrow, p.N, tid, THREADS);
+    stage_row_out<T>(s_out, dxrow, N, tid, THREADS);
   }
   if (tid == 0 && cta_abort) linger_after_abort();
 }

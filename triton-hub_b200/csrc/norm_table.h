@@ -19,14 +19,13 @@ struct PacketKernel {
   int threads() const { return 32 * warps_m * warps_n; }
 };
 
-// Launch shapes of the any-alignment row kernels: the first whose threads * columns-per-thread
-// covers the row is used.
-struct RowShape {
-  int threads, columns;
-};
+// The any-alignment row kernels: rows of up to kWarpRowSizes[2] elements take the warp-per-row
+// kernels, longer ones the kernels that stage a row through shared memory, with kRowThreads[i]
+// threads per row ([0] up to kRowSplit elements, [1] beyond).
 constexpr int kWarpRowSizes[3] = {256, 512, 1024};  // 32 lanes x 8 / 16 / 32 elements
-constexpr int kRowShapeCount = 6;
-constexpr RowShape kRowShapes[kRowShapeCount] = {{256, 4}, {256, 8}, {256, 16}, {256, 24}, {256, 32}, {1024, 32}};
+constexpr int kRowShapeCount = 2;
+constexpr int kRowThreads[kRowShapeCount] = {256, 512};
+constexpr int kRowSplit = 8192;
 
 struct DTypeKernels {
   int elem_size;
