@@ -172,6 +172,96 @@ def test_row_strided_and_non_contiguous_inputs():
     assert torch.equal(y1, y2)
 
 
+@pytest.mark.parametrize("rms", [False, True])
+@pytest.mark.parametrize("dtype,N,M", [("bf16", 4097, 2600), ("bf16", 1025, 3000), ("fp16", 2050, 2400), ("fp32", 1027, 2400),
+                                       ("fp32", 4101, 1300), ("fp64", 1031, 1300), ("bf16", 12289, 700),
+                                       ("bf16", 16391, 400), ("fp32", 16383, 400), ("bf16", 20001, 300)])
+def test_rows_of_odd_length_in_contiguous_tensors(dtype, N, M, rms):
+    """Contiguous rows of an odd length: x, dy, y and dx start every row at the same offset within a
+    16-byte line, which the vector row kernels need; more rows than resident CTAs, so that every CTA
+    walks several rows (all with the same alignment, by the grid's size)."""
+    x, dy, w, b = make_inputs(M, N, dtype, seed=N, has_b=not rms)
+    check_against_oracle(x, dy, w, b, 1e-5, rms=rms, dtype=dtype, label=f"N={N} ")
+
+
+@pytest.mark.parametrize("has_w,has_b", [(True, False), (False, False), (False, True)])
+def test_rows_of_odd_length_optional_parameters_and_fp32_parameters(has_w, has_b):
+    x, dy, w, b = make_inputs(900, 4099, "bf16", has_w=has_w, has_b=has_b)
+    check_against_oracle(x, dy, w, b, 1e-6, rms=False, dtype="bf16")
+    x, dy, w, _ = make_inputs(900, 2051, "fp16", has_w=has_w, has_b=False)
+    check_against_oracle(x, dy, w, None, 1e-6, rms=True, dtype="fp16")
+    x, dy, _, _ = make_inputs(900, 4099, "bf16")
+    _, _, w, b = make_inputs(1, 4099, "fp32", seed=5)
+    check_against_oracle(x, dy, w, b, 1e-5, rms=False, dtype="bf16", wdtype="fp32")
+    _, _, w, b = make_inputs(1, 4099, "fp64", seed=6)
+    check_against_oracle(x, dy, w, None, 1e-5, rms=True, dtype="bf16", wdtype="fp64")
+
+
+def test_row_shards_with_rows_of_odd_length():
+    """dweight / dbias of one launch over 8 shards == those of 8 launches over one shard each, also
+    through the vector row kernels (shards of 600 rows start at the same alignment)."""
+    M, N, S = 8 * 600, 4097, 8
+    x, dy, w, b = make_inputs(M, N, "bf16")
+    check_against_oracle(x, dy, w, b, 1e-6, rms=False, dtype="bf16", row_shards=S)
+    xt, dyt, wt, bt = (to_torch(a, "bf16", DEV) for a in (x, dy, w, b))
+    y, mean, rstd = Fn._layernorm_fwd(xt, wt, bt, 1e-6)
+    dx, dw, db, gs = Fn._layernorm_bwd(xt, dyt, wt, bt, mean, rstd, 1e-6, row_shards=S, group_sums=True)
+    R = M // S
+    parts = []
+    for s in range(S):
+        sl = slice(s * R, (s + 1) * R)
+        parts.append(Fn._layernorm_bwd(xt[sl], dyt[sl], wt, bt, mean[sl], rstd[sl], 1e-6, group_sums=True)[3])
+    gathered = torch.cat(parts, 0).contiguous()
+    assert torch.equal(gathered, gs)
+    outs = Fn.finalize_dwdb(gathered, torch.bfloat16)
+    assert torch.equal(outs[0], dw) and torch.equal(outs[1], db)
+
+
+@pytest.mark.parametrize("offset,stride", [(3, 4096 + 16), (1, 4096 + 5), (4, 4096)])
+def test_offset_views_through_the_c_abi(offset, stride):
+    """Views that start `offset` elements into their buffers (x, y, dy and dx alike, so every row has
+    the same alignment in all four) against the same rows in aligned buffers; and the same x with an
+    aligned y, whose rows are aligned differently (the kernels that stage whole rows)."""
+    M, N = 1500, 4096
+    torch.manual_seed(offset)
+    lib = _lib.load()
+
+    def view():
+        return torch.randn(M * stride + 32, device=DEV).bfloat16()[offset:offset + M * stride].view(M, stride)[:, :N]
+
+    x, dy, y, dx = view(), view(), view(), view()
+    w = torch.randn(N, device=DEV).bfloat16()
+    b = torch.randn(N, device=DEV).bfloat16()
+    mean = torch.empty(M, device=DEV)
+    rstd = torch.empty(M, device=DEV)
+    code = Fn._code(x, "input")
+    stream = torch.cuda.current_stream().cuda_stream
+    _lib.check(lib.b200norm_ln_fwd(x.data_ptr(), stride, w.data_ptr(), b.data_ptr(), y.data_ptr(), stride,
+                                   mean.data_ptr(), rstd.data_ptr(), M, N, 1e-5, code, code, stream))
+    yc, meanc, rstdc = Fn._layernorm_fwd(x.contiguous(), w, b, 1e-5)
+    torch.testing.assert_close(y.float(), yc.float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(mean, meanc, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(rstd, rstdc, rtol=1e-5, atol=1e-5)
+    ws_bytes = lib.b200norm_bwd_workspace_bytes(M, N, code, 1)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=DEV)
+    dw = torch.empty(N, device=DEV, dtype=torch.bfloat16)
+    db = torch.empty(N, device=DEV, dtype=torch.bfloat16)
+    _lib.check(lib.b200norm_ln_bwd(x.data_ptr(), stride, dy.data_ptr(), stride, w.data_ptr(), meanc.data_ptr(),
+                                   rstdc.data_ptr(), dx.data_ptr(), stride, dw.data_ptr(), db.data_ptr(), None, 1,
+                                   ws.data_ptr(), ws_bytes, M, N, code, code, stream))
+    dxc, dwc, dbc = Fn._layernorm_bwd(x.contiguous(), dy.contiguous(), w, b, meanc, rstdc, 1e-5)
+    torch.testing.assert_close(dx.float(), dxc.float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(dw.float(), dwc.float(), rtol=2e-2, atol=0.3)
+    torch.testing.assert_close(db.float(), dbc.float(), rtol=2e-2, atol=0.3)
+    # x in the view, y and dx aligned: rows aligned differently in the two
+    y2, mean2, rstd2 = Fn._layernorm_fwd(x, w, b, 1e-5)
+    torch.testing.assert_close(y2.float(), yc.float(), rtol=1e-2, atol=1e-2)
+    dx2, dw2, db2 = Fn._layernorm_bwd(x, dy.contiguous(), w, b, meanc, rstdc, 1e-5)
+    torch.testing.assert_close(dx2.float(), dxc.float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(dw2.float(), dwc.float(), rtol=2e-2, atol=0.3)
+    assert lib.b200norm_device_status(0) == 0
+
+
 def test_batch_shape_is_restored():
     m = LayerNorm(128, eps=1e-6, device=DEV, dtype=torch.float32)
     x = torch.randn(2, 100, 128, device=DEV, requires_grad=True)

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <numeric>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -266,6 +267,59 @@ int launch_row_kernel(DeviceState& dev, const void* const (&fns)[kRowShapeCount]
   return launch(fn, dim3(grid), dim3(threads), smem, params, stream, false);
 }
 
+// Whether two buffers start every row at the same offset within a 16-byte line.
+bool same_phase(const void* a, int64_t sa, const void* b, int64_t sb, int es) {
+  return ((reinterpret_cast<uintptr_t>(a) ^ reinterpret_cast<uintptr_t>(b)) & 15u) == 0 && ((sa - sb) * es) % 16 == 0;
+}
+
+// After how many rows the offset of a row within a 16-byte line repeats.
+int phase_period(int64_t stride, int es) {
+  const int r = static_cast<int>((stride * es) % 16);
+  return r == 0 ? 1 : 16 / std::gcd(16, r);
+}
+
+// Ring slots of a vector row kernel (norm_rows_any.cuh) and its dynamic shared memory; 0 when two
+// slots do not fit.  Small footprints first: several CTAs per SM hide the per-row reductions.
+int vrow_slots(int64_t N, int es, int rows_per_slot, int param_vectors, int w_dtype, size_t* smem) {
+  const size_t interior = vrow_interior_bytes(N, es) * rows_per_slot;
+  const size_t params = vrow_param_bytes(N, w_dtype) * param_vectors;
+  const size_t caps[3] = {72 * 1024, 112 * 1024, kMaxSmemPerCta - 4096};
+  for (size_t cap : caps)
+    for (int slots = 4; slots >= 2; --slots)
+      if (slots * interior + params <= cap) {
+        *smem = slots * interior + params;
+        return slots;
+      }
+  return 0;
+}
+
+// CTAs (per shard) of a vector row kernel: every row its own CTA while they are all resident, else
+// the resident count rounded down to the period of the rows' alignment, so that all rows of a CTA
+// are aligned alike.
+int64_t vrow_ctas(int64_t rows, int64_t resident, int period) {
+  if (rows <= resident) return rows;
+  return resident / period * period;
+}
+
+// Forward through the vector row kernel when x and y share their rows' alignment; *done says whether
+// it was launched.
+int launch_vrow_fwd(DeviceState& dev, const DTypeKernels* k, int op, FwdParams& p, int es, cudaStream_t stream, bool* done) {
+  *done = false;
+  if (p.N <= kWarpRowSizes[2] || !same_phase(p.x, p.x_stride, p.y, p.y_stride, es)) return B200NORM_OK;
+  size_t smem;
+  const int slots = vrow_slots(p.N, es, 1, 2, p.w_dtype, &smem);
+  const int shape = (int64_t)p.N * es / 16 <= kVRowSplit ? 0 : 1;
+  const void* fn = k->fwd_vrows[op][shape];
+  if (slots == 0 || fn == nullptr) return B200NORM_OK;
+  int occ;
+  if (int rc = occupancy(dev, fn, kRowThreads[shape], smem, &occ)) return rc;
+  const int64_t grid = vrow_ctas(p.M, (int64_t)dev.sm_count * occ, phase_period(p.x_stride, es));
+  if (grid < 1) return B200NORM_OK;
+  p.V = slots;
+  *done = true;
+  return launch(fn, dim3(static_cast<unsigned>(grid)), dim3(kRowThreads[shape]), smem, &p, stream, false);
+}
+
 int check_common(int64_t M, int64_t N, int io_dtype, int w_dtype) {
   if (!valid_dtype(io_dtype) || !valid_dtype(w_dtype))
     return fail(B200NORM_ERR_ARG, "unknown dtype code (io %d, w %d)", io_dtype, w_dtype);
@@ -315,6 +369,9 @@ int fwd_impl(int op, const void* x, int64_t xs, const void* w, const void* b, vo
     return fail(B200NORM_ERR_UNSUPPORTED,
                 "a fused activation needs rows whose base, stride and length are multiples of 16 bytes; run the norm "
                 "and b200norm_gelu_fwd separately");
+  bool done;
+  if (int rc = launch_vrow_fwd(*dev, k, op, p, es, static_cast<cudaStream_t>(stream), &done)) return rc;
+  if (done) return B200NORM_OK;
   return launch_row_kernel(*dev, k->fwd_rows[op], k->fwd_warp_rows[op], M, N, es, 1, &p, static_cast<cudaStream_t>(stream));
 }
 
@@ -323,7 +380,21 @@ struct BwdPlan {
   const PacketKernel* pk;  // null: any-alignment kernels
   int ctas_per_shard;
   size_t smem;
+  const void* vrow;  // any alignment: the vector row kernel (dx and partial rows in one), or null
+  int vrow_threads, vrow_slots;
 };
+
+// The buffers of a backward call, for the choice among the any-alignment kernels.
+struct BwdBuffers {
+  const void *x, *dy, *dx;
+  int64_t xs, dys, dxs;
+  int w_dtype;
+};
+
+// Upper bound of the partial rows per shard of a vector row kernel (256 threads, 2048 per SM).
+int64_t vrow_ctas_bound(const DeviceState& dev, int64_t rows_per_shard) {
+  return std::min<int64_t>(rows_per_shard, (int64_t)dev.sm_count * 8);
+}
 
 // Partial rows per shard of the any-alignment dweight / dbias kernel (one thread per column, one CTA
 // per 256 columns and partial row): enough CTAs to fill the GPU twice over whatever the row length,
@@ -335,12 +406,33 @@ int any_ctas_per_shard(int64_t rows_per_shard, int64_t N) {
 }
 
 int plan_bwd(DeviceState& dev, const DTypeKernels* k, int op, int64_t rows_per_shard, int64_t N, bool packets,
-             BwdPlan* plan, int act = 0) {
+             BwdPlan* plan, int act = 0, const BwdBuffers* bufs = nullptr) {
   const int es = k->elem_size;
   plan->pk = packets ? pick(k->bwd[op], k->n_bwd[op], N * es / 16, true, N, es, act) : nullptr;
+  plan->vrow = nullptr;
   if (plan->pk == nullptr) {
     plan->ctas_per_shard = any_ctas_per_shard(rows_per_shard, N);
     plan->smem = 0;
+    if (bufs == nullptr || act != 0 || rows_per_shard < 1 || N <= kWarpRowSizes[2] ||
+        !same_phase(bufs->x, bufs->xs, bufs->dy, bufs->dys, es) || !same_phase(bufs->x, bufs->xs, bufs->dx, bufs->dxs, es))
+      return B200NORM_OK;
+    size_t smem;
+    const int slots = vrow_slots(N, es, 2, 1, bufs->w_dtype, &smem);
+    if (slots == 0) return B200NORM_OK;
+    for (int i = 0; i < kVRowShapeCount; ++i) {
+      const void* fn = k->bwd_vrows[op][i];
+      if (fn == nullptr || (int64_t)kVRowShapes[i].threads * kVRowShapes[i].packets < N * es / 16) continue;
+      int occ;
+      if (int rc = occupancy(dev, fn, kVRowShapes[i].threads, smem, &occ)) return rc;
+      const int64_t ctas = vrow_ctas(rows_per_shard, (int64_t)dev.sm_count * occ, phase_period(bufs->xs, es));
+      if (ctas < 1 || ctas > vrow_ctas_bound(dev, rows_per_shard)) return B200NORM_OK;
+      plan->vrow = fn;
+      plan->vrow_threads = kVRowShapes[i].threads;
+      plan->vrow_slots = slots;
+      plan->smem = smem;
+      plan->ctas_per_shard = static_cast<int>(ctas);
+      return B200NORM_OK;
+    }
     return B200NORM_OK;
   }
   const PacketKernel* pk = plan->pk;
@@ -430,7 +522,8 @@ int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, con
   const bool packets =
       (N * es) % 16 == 0 && aligned16(x, xs, es) && aligned16(dy, dys, es) && aligned16(dx, dxs, es);
   BwdPlan plan;
-  if (int rc = plan_bwd(*dev, k, op, M / row_shards, N, packets, &plan, act)) return rc;
+  const BwdBuffers bufs = {x, dy, dx, xs, dys, dxs, w_dtype};
+  if (int rc = plan_bwd(*dev, k, op, M / row_shards, N, packets, &plan, act, &bufs)) return rc;
   if (act != 0 && plan.pk == nullptr)
     return fail(B200NORM_ERR_UNSUPPORTED,
                 "a fused activation needs rows whose base, stride and length are multiples of 16 bytes; run "
@@ -459,6 +552,10 @@ int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, con
   if (plan.pk != nullptr) {
     if (int rc = launch(plan.pk->fn, dim3(static_cast<unsigned>(P * plan.pk->cluster)), dim3(plan.pk->threads()),
                         plan.smem, &p, stream, true, plan.pk->cluster))
+      return rc;
+  } else if (plan.vrow != nullptr) {
+    p.V = plan.vrow_slots;
+    if (int rc = launch(plan.vrow, dim3(static_cast<unsigned>(P)), dim3(plan.vrow_threads), plan.smem, &p, stream, false))
       return rc;
   } else {
     if (M > 0) {
@@ -786,6 +883,7 @@ size_t b200norm_bwd_workspace_bytes(int64_t M, int64_t N, int io_dtype, int row_
   const DTypeKernels* k = kernels_for(io_dtype);
   const int64_t rps = M / row_shards;
   int64_t per_shard = any_ctas_per_shard(rps, N);
+  if (N > kWarpRowSizes[2]) per_shard = std::max(per_shard, vrow_ctas_bound(*dev, rps));  // misaligned views of any N
   if ((N * k->elem_size) % 16 == 0) {
     // LayerNorm and RMSNorm instantiations may differ in occupancy: take the larger.
     // and with or without a fused activation

@@ -346,6 +346,434 @@ __global__ void __launch_bounds__(THREADS) norm_bwd_dx_row_kernel(const BwdParam
 }
 
 // ---------------------------------------------------------------------------------------
+// Vector kernels for rows whose buffers SHARE one alignment: x and y (forward), or x, dy and dx
+// (backward), start every row at the same offset within a 16-byte line -- rows of an odd length in
+// contiguous tensors from one allocator, offset views of such tensors.  Then a row's 16-byte
+// interior is made of the same columns in every buffer, and the packet arithmetic of the aligned
+// kernels applies to it:
+//
+//   * the interior of each row is staged by one bulk asynchronous copy into a ring of shared-memory
+//     slots and read from there with 128-bit loads; results go to global memory with 128-bit
+//     stores straight from registers;
+//   * the up to 2 * (16 / sizeof(T) - 1) elements before and after the interior belong to one thread
+//     each of the CTA's last warp, which reads them from global memory a row ahead;
+//   * the host sizes the grid so that all rows of a CTA have the same alignment (the alignment of
+//     rows repeats with a period of at most 16 / sizeof(T) rows); the parameter vectors are copied
+//     once per CTA into shared memory, shifted so that they line up with the interior's packets;
+//   * backward: the CTA carries dweight / dbias of its columns in registers across its rows and
+//     writes one partial row, like the packet kernels -- x and dy are read once.
+//
+// p.V carries the number of ring slots.  Dynamic shared memory: slots * (1 or 2) row interiors of
+// (N * sizeof(T) / 16) * 16 bytes, then one (backward) or two (forward) parameter vectors of
+// vrow_param_bytes() each.
+// ---------------------------------------------------------------------------------------
+__host__ __device__ inline size_t vrow_interior_bytes(int64_t N, int es) { return static_cast<size_t>(N * es / 16) * 16; }
+__host__ __device__ inline int param_elem_size(int dtype) { return dtype == kF32 ? 4 : dtype == kF64 ? 8 : 2; }
+__host__ __device__ inline size_t vrow_param_bytes(int64_t N, int w_dtype) {
+  return (static_cast<size_t>(N) * param_elem_size(w_dtype) + 15) & ~static_cast<size_t>(15);
+}
+
+// EPP parameter values of storage type P, packet v of the shifted copy in shared memory.
+template <typename P, int EPP>
+__device__ __forceinline__ void ld_param_chunk(const unsigned char* base, int v, float2 (&out)[EPP / 2]) {
+  struct alignas((sizeof(P) * EPP > 16) ? 16 : sizeof(P) * EPP) Chunk {
+    P e[EPP];
+  };
+  const Chunk c = reinterpret_cast<const Chunk*>(base)[v];
+#pragma unroll
+  for (int i = 0; i < EPP / 2; ++i) out[i] = make_float2(to_f32(c.e[2 * i]), to_f32(c.e[2 * i + 1]));
+}
+
+// dst[i] = src[i], i < n, element by element (the source has no alignment to speak of).
+template <typename U>
+__device__ __forceinline__ void copy_elements(void* dst, const void* src, int n, int tid, int nthreads) {
+#pragma unroll 8
+  for (int i = tid; i < n; i += nthreads) static_cast<U*>(dst)[i] = __ldg(static_cast<const U*>(src) + i);
+}
+__device__ __forceinline__ void stage_params(unsigned char* dst, const void* src, int first, int n, int dtype, int tid,
+                                             int nthreads) {
+  const unsigned char* from = static_cast<const unsigned char*>(src) + (size_t)first * param_elem_size(dtype);
+  if (dtype == kF32) copy_elements<uint32_t>(dst, from, n, tid, nthreads);
+  else if (dtype == kF64) copy_elements<unsigned long long>(dst, from, n, tid, nthreads);
+  else copy_elements<unsigned short>(dst, from, n, tid, nthreads);
+}
+__device__ __forceinline__ float param_scalar(const void* p, int dtype, int c, float fill) {
+  if (p == nullptr) return fill;
+  switch (dtype) {
+    case kF32: return param_at<float>(p, c);
+    case kF16: return param_at<__half>(p, c);
+    case kBF16: return param_at<__nv_bfloat16>(p, c);
+    default: return param_at<double>(p, c);
+  }
+}
+
+// The output pass of the forward kernel over the interior packets of one row.
+template <typename T, typename P, int THREADS, bool HAS_W, bool HAS_B>
+__device__ __forceinline__ void vrow_fwd_out(const uint4* xs4, const unsigned char* s_w, const unsigned char* s_b,
+                                             uint4* ybody, int VB, int tid, float mean, float rstd) {
+  constexpr int EPP = Pack16<T>::kElems, H = EPP / 2;
+  const float2 nm = splat2(-mean), rs = splat2(rstd);
+#pragma unroll 2
+  for (int v = tid; v < VB; v += THREADS) {
+    float2 f[H], w[H], b[H];
+    Pack16<T>::unpack2(xs4[v], f);
+    if (HAS_W) ld_param_chunk<P, EPP>(s_w, v, w);
+    if (HAS_B) ld_param_chunk<P, EPP>(s_b, v, b);
+#pragma unroll
+    for (int h = 0; h < H; ++h) {
+      float2 t = mul2(add2(f[h], nm), rs);
+      if (HAS_W && HAS_B) t = fma2(t, w[h], b[h]);
+      else if (HAS_W) t = mul2(t, w[h]);
+      else if (HAS_B) t = add2(t, b[h]);
+      f[h] = t;
+    }
+    st_stream(ybody + v, Pack16<T>::pack2(f));
+  }
+}
+template <typename T, typename P, int THREADS>
+__device__ __forceinline__ void vrow_fwd_out_any(bool has_w, bool has_b, const uint4* xs4, const unsigned char* s_w,
+                                                 const unsigned char* s_b, uint4* ybody, int VB, int tid, float mean,
+                                                 float rstd) {
+  if (has_w && has_b) vrow_fwd_out<T, P, THREADS, true, true>(xs4, s_w, s_b, ybody, VB, tid, mean, rstd);
+  else if (has_w) vrow_fwd_out<T, P, THREADS, true, false>(xs4, s_w, s_b, ybody, VB, tid, mean, rstd);
+  else if (has_b) vrow_fwd_out<T, P, THREADS, false, true>(xs4, s_w, s_b, ybody, VB, tid, mean, rstd);
+  else vrow_fwd_out<T, P, THREADS, false, false>(xs4, s_w, s_b, ybody, VB, tid, mean, rstd);
+}
+
+template <typename T, int THREADS, bool RMS>
+__global__ void __launch_bounds__(THREADS) norm_fwd_vrow_kernel(const FwdParams p) {
+  constexpr int WARPS = THREADS / 32;
+  constexpr int ES = static_cast<int>(sizeof(T)), EPP = Pack16<T>::kElems, H = EPP / 2;
+  extern __shared__ __align__(128) unsigned char dyn_smem[];
+  __shared__ float red[2 * WARPS];
+  __shared__ __align__(8) uint64_t full_bar[kRowStagesMax];
+  __shared__ int cta_abort;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int N = p.N, stages = p.V;
+  const size_t slot_bytes = vrow_interior_bytes(N, ES);
+  const T* xb = static_cast<const T*>(p.x);
+  T* yb = static_cast<T*>(p.y);
+  const int64_t row0 = blockIdx.x, step = gridDim.x;
+  // the same for every row of this CTA
+  const RowSpan<T> sp(xb + row0 * p.x_stride, N);
+  const int VB = sp.body_bytes / 16;
+  const int edges = sp.head + (N - sp.tail0);
+  unsigned char* s_w = dyn_smem + (size_t)stages * slot_bytes;
+  unsigned char* s_b = s_w + vrow_param_bytes(N, p.w_dtype);
+  const bool has_w = p.w != nullptr, has_b = !RMS && p.b != nullptr;
+  int phase_bit = 0;
+
+  auto fill = [&](int slot, int64_t row) {  // the leader only
+    mbar_expect_tx(&full_bar[slot], static_cast<uint32_t>(sp.body_bytes));
+    bulk_load(dyn_smem + (size_t)slot * slot_bytes, xb + row * p.x_stride + sp.head, static_cast<uint32_t>(sp.body_bytes),
+              &full_bar[slot]);
+  };
+
+  if (tid == 0) {
+    for (int i = 0; i < kRowStagesMax; ++i) mbar_init(&full_bar[i], 1);
+    cta_abort = 0;
+    mbar_init_fence();
+    for (int s = 0; s < stages; ++s) {
+      const int64_t r = row0 + (int64_t)s * step;
+      if (r < p.M) fill(s, r);
+    }
+  }
+  // this thread's edge element, if it has one
+  const int ej = tid - (THREADS - 32);
+  const bool is_edge = ej >= 0 && ej < edges;
+  const int ecol = is_edge ? (ej < sp.head ? ej : sp.tail0 + (ej - sp.head)) : 0;
+  float xe_next = 0.f, we = 1.f, be = 0.f;
+  if (is_edge) {
+    xe_next = to_f32(xb[row0 * p.x_stride + ecol]);
+    we = param_scalar(p.w, p.w_dtype, ecol, 1.f);
+    be = RMS ? 0.f : param_scalar(p.b, p.w_dtype, ecol, 0.f);
+  }
+  if (has_w) stage_params(s_w, p.w, sp.head, VB * EPP, p.w_dtype, tid, THREADS);
+  if (has_b) stage_params(s_b, p.b, sp.head, VB * EPP, p.w_dtype, tid, THREADS);
+  __syncthreads();  // barriers initialised, parameters in place
+
+  const float inv_n = 1.f / static_cast<float>(N);
+  int slot = 0, prev_slot = -1;
+  uint32_t parity = 0;
+  for (int64_t row = row0; row < p.M; row += step) {
+    const float xe = xe_next;
+    if (is_edge && row + step < p.M) xe_next = to_f32(xb[(row + step) * p.x_stride + ecol]);
+    mbar_wait(&full_bar[slot], parity, &cta_abort, p.status);
+    const uint4* xs4 = reinterpret_cast<const uint4*>(dyn_smem + (size_t)slot * slot_bytes);
+    float mean = 0.f;
+    if (!RMS) {
+      float2 a = splat2(0.f);
+#pragma unroll 4
+      for (int v = tid; v < VB; v += THREADS) {
+        float2 f[H];
+        Pack16<T>::unpack2(xs4[v], f);
+#pragma unroll
+        for (int h = 0; h < H; ++h) a = add2(a, f[h]);
+      }
+      float s[1] = {a.x + a.y + (is_edge ? xe : 0.f)};
+      group_sum<WARPS, 1, 0>(s, red, phase_bit, 0, warp, lane);
+      mean = s[0] * inv_n;
+    }
+    float2 q2 = splat2(0.f);
+    {
+      const float2 nm = splat2(-mean);
+#pragma unroll 4
+      for (int v = tid; v < VB; v += THREADS) {
+        float2 f[H];
+        Pack16<T>::unpack2(xs4[v], f);
+#pragma unroll
+        for (int h = 0; h < H; ++h) {
+          const float2 d = RMS ? f[h] : add2(f[h], nm);
+          q2 = fma2(d, d, q2);
+        }
+      }
+    }
+    float q[1] = {q2.x + q2.y + (is_edge ? (xe - mean) * (xe - mean) : 0.f)};
+    group_sum<WARPS, 1, 0>(q, red, phase_bit, 0, warp, lane);
+    // every thread is past the previous row's output pass: its slot can take the row `stages` on
+    if (tid == 0 && prev_slot >= 0) {
+      const int64_t r = row + (int64_t)(stages - 1) * step;
+      if (r < p.M) fill(prev_slot, r);
+    }
+    const float rstd = 1.f / sqrtf(q[0] * inv_n + p.eps);
+    if (tid == 0) {
+      if (!RMS) p.mean[row] = mean;
+      p.rstd[row] = rstd;
+    }
+    T* yrow = yb + row * p.y_stride;
+    uint4* ybody = reinterpret_cast<uint4*>(yrow + sp.head);
+    switch (p.w_dtype) {
+      case kF32: vrow_fwd_out_any<T, float, THREADS>(has_w, has_b, xs4, s_w, s_b, ybody, VB, tid, mean, rstd); break;
+      case kF16: vrow_fwd_out_any<T, __half, THREADS>(has_w, has_b, xs4, s_w, s_b, ybody, VB, tid, mean, rstd); break;
+      case kBF16: vrow_fwd_out_any<T, __nv_bfloat16, THREADS>(has_w, has_b, xs4, s_w, s_b, ybody, VB, tid, mean, rstd); break;
+      default: vrow_fwd_out_any<T, double, THREADS>(has_w, has_b, xs4, s_w, s_b, ybody, VB, tid, mean, rstd); break;
+    }
+    if (is_edge) yrow[ecol] = from_f32<T>((xe - mean) * rstd * we + be);
+    prev_slot = slot;
+    if (++slot == stages) {
+      slot = 0;
+      parity ^= 1u;
+    }
+  }
+  if (tid == 0 && cta_abort) linger_after_abort();
+}
+
+// The two passes of the backward kernel over the interior packets of one row.
+template <typename T, typename P, int THREADS, int K, bool RMS, bool HAS_W>
+__device__ __forceinline__ void vrow_bwd_sums(const uint4* xs4, const uint4* gs4, const unsigned char* s_w, int VB, int tid,
+                                              float mu, float rs, float2 (&acc_w)[K][Pack16<T>::kElems / 2],
+                                              float2 (&acc_b)[K][Pack16<T>::kElems / 2], float2& s0, float2& s1) {
+  constexpr int EPP = Pack16<T>::kElems, H = EPP / 2;
+  const float2 nm = splat2(-mu), r2 = splat2(rs);
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const int v = tid + k * THREADS;
+    if (v < VB) {
+      float2 x[H], g[H], w[H];
+      Pack16<T>::unpack2(xs4[v], x);
+      Pack16<T>::unpack2(gs4[v], g);
+      if (HAS_W) ld_param_chunk<P, EPP>(s_w, v, w);
+#pragma unroll
+      for (int h = 0; h < H; ++h) {
+        const float2 xh = RMS ? mul2(x[h], r2) : mul2(add2(x[h], nm), r2);
+        const float2 wdy = HAS_W ? mul2(w[h], g[h]) : g[h];
+        s0 = fma2(xh, wdy, s0);
+        if (!RMS) s1 = add2(s1, wdy);
+        acc_w[k][h] = fma2(g[h], xh, acc_w[k][h]);
+        if (!RMS) acc_b[k][h] = add2(acc_b[k][h], g[h]);
+      }
+    }
+  }
+}
+template <typename T, typename P, int THREADS, int K, bool RMS, bool HAS_W>
+__device__ __forceinline__ void vrow_bwd_dx(const uint4* xs4, const uint4* gs4, const unsigned char* s_w, uint4* dxbody,
+                                            int VB, int tid, float mu, float rs, float c1, float c2) {
+  constexpr int EPP = Pack16<T>::kElems, H = EPP / 2;
+  const float2 nm = splat2(-mu), r2 = splat2(rs), nc1 = splat2(-c1), nc2 = splat2(-c2);
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const int v = tid + k * THREADS;
+    if (v < VB) {
+      float2 x[H], g[H], w[H];
+      Pack16<T>::unpack2(xs4[v], x);
+      Pack16<T>::unpack2(gs4[v], g);
+      if (HAS_W) ld_param_chunk<P, EPP>(s_w, v, w);
+#pragma unroll
+      for (int h = 0; h < H; ++h) {
+        const float2 xh = RMS ? mul2(x[h], r2) : mul2(add2(x[h], nm), r2);
+        const float2 wdy = HAS_W ? mul2(w[h], g[h]) : g[h];
+        x[h] = mul2(add2(wdy, fma2(xh, nc1, nc2)), r2);  // (wdy - (xh * c1 + c2)) * rstd
+      }
+      st_stream(dxbody + v, Pack16<T>::pack2(x));
+    }
+  }
+}
+
+template <typename T, int THREADS, int K, bool RMS>
+__global__ void __launch_bounds__(THREADS) norm_bwd_vrow_kernel(const BwdParams p) {
+  constexpr int WARPS = THREADS / 32;
+  constexpr int NV = RMS ? 1 : 2;
+  constexpr int ES = static_cast<int>(sizeof(T)), EPP = Pack16<T>::kElems, H = EPP / 2;
+  extern __shared__ __align__(128) unsigned char dyn_smem[];
+  __shared__ float red[2 * NV * WARPS];
+  __shared__ __align__(8) uint64_t full_bar[kRowStagesMax];
+  __shared__ int cta_abort;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int N = p.N, stages = p.V;
+  const size_t slot_bytes = vrow_interior_bytes(N, ES);
+  const T* xb = static_cast<const T*>(p.x);
+  const T* gb = static_cast<const T*>(p.dy);
+  T* db = static_cast<T*>(p.dx);
+  // row shards as in the packet kernels: CTA c serves shard c / ctas_per_shard, rows strided by ctas_per_shard
+  const int shard = blockIdx.x / p.ctas_per_shard;
+  const int64_t shard_begin = (int64_t)shard * p.rows_per_shard;
+  const int64_t shard_end = min(shard_begin + p.rows_per_shard, p.M);
+  const int64_t row0 = shard_begin + (blockIdx.x - shard * p.ctas_per_shard), step = p.ctas_per_shard;
+  float* dw_row = p.dw_part != nullptr ? p.dw_part + (size_t)blockIdx.x * N : nullptr;
+  float* db_row = (!RMS && p.db_part != nullptr) ? p.db_part + (size_t)blockIdx.x * N : nullptr;
+  if (row0 >= shard_end) {  // no row for this CTA: its partial rows are zero
+    for (int c = tid; c < N; c += THREADS) {
+      if (dw_row != nullptr) dw_row[c] = 0.f;
+      if (db_row != nullptr) db_row[c] = 0.f;
+    }
+    return;
+  }
+  const RowSpan<T> sp(xb + row0 * p.x_stride, N);
+  const int VB = sp.body_bytes / 16;
+  const int edges = sp.head + (N - sp.tail0);
+  unsigned char* s_w = dyn_smem + (size_t)(2 * stages) * slot_bytes;
+  const bool has_w = p.w != nullptr;
+  int phase_bit = 0;
+
+  auto fill = [&](int slot, int64_t row) {  // the leader only
+    mbar_expect_tx(&full_bar[slot], static_cast<uint32_t>(2 * sp.body_bytes));
+    unsigned char* shx = dyn_smem + (size_t)(2 * slot) * slot_bytes;
+    bulk_load(shx, xb + row * p.x_stride + sp.head, static_cast<uint32_t>(sp.body_bytes), &full_bar[slot]);
+    bulk_load(shx + slot_bytes, gb + row * p.dy_stride + sp.head, static_cast<uint32_t>(sp.body_bytes), &full_bar[slot]);
+  };
+
+  if (tid == 0) {
+    for (int i = 0; i < kRowStagesMax; ++i) mbar_init(&full_bar[i], 1);
+    cta_abort = 0;
+    mbar_init_fence();
+    for (int s = 0; s < stages; ++s) {
+      const int64_t r = row0 + (int64_t)s * step;
+      if (r < shard_end) fill(s, r);
+    }
+  }
+  const int ej = tid - (THREADS - 32);
+  const bool is_edge = ej >= 0 && ej < edges;
+  const int ecol = is_edge ? (ej < sp.head ? ej : sp.tail0 + (ej - sp.head)) : 0;
+  float xe_next = 0.f, ge_next = 0.f, we = 1.f;
+  if (is_edge) {
+    xe_next = to_f32(xb[row0 * p.x_stride + ecol]);
+    ge_next = to_f32(gb[row0 * p.dy_stride + ecol]);
+    we = param_scalar(p.w, p.w_dtype, ecol, 1.f);
+  }
+  float mu_next = RMS ? 0.f : __ldg(p.mean + row0);
+  float rs_next = __ldg(p.rstd + row0);
+  if (has_w) stage_params(s_w, p.w, sp.head, VB * EPP, p.w_dtype, tid, THREADS);
+  __syncthreads();  // barriers initialised, weight in place
+
+  float2 acc_w[K][H], acc_b[K][H];
+#pragma unroll
+  for (int k = 0; k < K; ++k)
+#pragma unroll
+    for (int h = 0; h < H; ++h) acc_w[k][h] = acc_b[k][h] = splat2(0.f);
+  float ew_acc = 0.f, eb_acc = 0.f;
+  const float inv_n = 1.f / static_cast<float>(N);
+  int slot = 0, prev_slot = -1;
+  uint32_t parity = 0;
+  for (int64_t row = row0; row < shard_end; row += step) {
+    const float xe = xe_next, ge = ge_next, mu = mu_next, rs = rs_next;
+    if (row + step < shard_end) {
+      if (is_edge) {
+        xe_next = to_f32(xb[(row + step) * p.x_stride + ecol]);
+        ge_next = to_f32(gb[(row + step) * p.dy_stride + ecol]);
+      }
+      if (!RMS) mu_next = __ldg(p.mean + row + step);
+      rs_next = __ldg(p.rstd + row + step);
+    }
+    mbar_wait(&full_bar[slot], parity, &cta_abort, p.status);
+    const uint4* xs4 = reinterpret_cast<const uint4*>(dyn_smem + (size_t)(2 * slot) * slot_bytes);
+    const uint4* gs4 = reinterpret_cast<const uint4*>(dyn_smem + (size_t)(2 * slot + 1) * slot_bytes);
+    float2 s0 = splat2(0.f), s1 = splat2(0.f);
+#define B200NORM_VROW_SUMS(P)                                                                                          \
+  if (has_w) vrow_bwd_sums<T, P, THREADS, K, RMS, true>(xs4, gs4, s_w, VB, tid, mu, rs, acc_w, acc_b, s0, s1);          \
+  else vrow_bwd_sums<T, P, THREADS, K, RMS, false>(xs4, gs4, s_w, VB, tid, mu, rs, acc_w, acc_b, s0, s1)
+    switch (p.w_dtype) {
+      case kF32: B200NORM_VROW_SUMS(float); break;
+      case kF16: B200NORM_VROW_SUMS(__half); break;
+      case kBF16: B200NORM_VROW_SUMS(__nv_bfloat16); break;
+      default: B200NORM_VROW_SUMS(double); break;
+    }
+#undef B200NORM_VROW_SUMS
+    float s[NV];
+    s[0] = s0.x + s0.y;
+    if (!RMS) s[NV - 1] = s1.x + s1.y;
+    float xh_e = 0.f, wdy_e = 0.f;
+    if (is_edge) {
+      xh_e = (xe - mu) * rs;
+      wdy_e = we * ge;
+      s[0] += xh_e * wdy_e;
+      if (!RMS) s[NV - 1] += wdy_e;
+      ew_acc += ge * xh_e;
+      eb_acc += ge;
+    }
+    group_sum<WARPS, NV, 0>(s, red, phase_bit, 0, warp, lane);
+    // every thread is past the previous row's dx pass: its slot can take the row `stages` on
+    if (tid == 0 && prev_slot >= 0) {
+      const int64_t r = row + (int64_t)(stages - 1) * step;
+      if (r < shard_end) fill(prev_slot, r);
+    }
+    const float c1 = s[0] * inv_n;
+    const float c2 = RMS ? 0.f : s[NV - 1] * inv_n;
+    T* dxrow = db + row * p.dx_stride;
+    uint4* dxbody = reinterpret_cast<uint4*>(dxrow + sp.head);
+#define B200NORM_VROW_DX(P)                                                                                  \
+  if (has_w) vrow_bwd_dx<T, P, THREADS, K, RMS, true>(xs4, gs4, s_w, dxbody, VB, tid, mu, rs, c1, c2);         \
+  else vrow_bwd_dx<T, P, THREADS, K, RMS, false>(xs4, gs4, s_w, dxbody, VB, tid, mu, rs, c1, c2)
+    switch (p.w_dtype) {
+      case kF32: B200NORM_VROW_DX(float); break;
+      case kF16: B200NORM_VROW_DX(__half); break;
+      case kBF16: B200NORM_VROW_DX(__nv_bfloat16); break;
+      default: B200NORM_VROW_DX(double); break;
+    }
+#undef B200NORM_VROW_DX
+    if (is_edge) dxrow[ecol] = from_f32<T>((wdy_e - (xh_e * c1 + c2)) * rs);
+    prev_slot = slot;
+    if (++slot == stages) {
+      slot = 0;
+      parity ^= 1u;
+    }
+  }
+  // this CTA's partial rows
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const int v = tid + k * THREADS;
+    if (v < VB) {
+      const int c = sp.head + v * EPP;
+#pragma unroll
+      for (int h = 0; h < H; ++h) {
+        if (dw_row != nullptr) {
+          dw_row[c + 2 * h] = acc_w[k][h].x;
+          dw_row[c + 2 * h + 1] = acc_w[k][h].y;
+        }
+        if (db_row != nullptr) {
+          db_row[c + 2 * h] = acc_b[k][h].x;
+          db_row[c + 2 * h + 1] = acc_b[k][h].y;
+        }
+      }
+    }
+  }
+  if (is_edge) {
+    if (dw_row != nullptr) dw_row[ecol] = ew_acc;
+    if (db_row != nullptr) db_row[ecol] = eb_acc;
+  }
+  if (tid == 0 && cta_abort) linger_after_abort();
+}
+
+// ---------------------------------------------------------------------------------------
 // Short rows of any alignment (at most 32 * K elements): one WARP per row, no shared memory.
 // Lane l takes elements l, l + 32, ...: a warp's access is one contiguous run of the row, the
 // K loads of a lane are all in flight at once, and the reductions are shuffles.  A CTA of eight
