@@ -281,7 +281,7 @@ int phase_period(int64_t stride, int es) {
 // Ring slots of a vector row kernel (norm_rows_any.cuh) and its dynamic shared memory; 0 when two
 // slots do not fit.  Small footprints first: several CTAs per SM hide the per-row reductions.
 int vrow_slots(int64_t N, int es, int rows_per_slot, int param_vectors, int w_dtype, size_t* smem) {
-  const size_t interior = vrow_interior_bytes(N, es) * rows_per_slot;
+  const size_t interior = vrow_interior_bytes(N, es) * rows_per_slot;  // of all the CTA's row groups
   const size_t params = vrow_param_bytes(N, w_dtype) * param_vectors;
   const size_t caps[3] = {72 * 1024, 112 * 1024, kMaxSmemPerCta - 4096};
   for (size_t cap : caps)
@@ -293,11 +293,15 @@ int vrow_slots(int64_t N, int es, int rows_per_slot, int param_vectors, int w_dt
   return 0;
 }
 
-// CTAs (per shard) of a vector row kernel: every row its own CTA while they are all resident, else
-// the resident count rounded down to the period of the rows' alignment, so that all rows of a CTA
-// are aligned alike.
-int64_t vrow_ctas(int64_t rows, int64_t resident, int period) {
-  if (rows <= resident) return rows;
+// CTAs (per shard) of a vector row kernel whose CTAs take `groups` rows at a time: enough for every
+// row while they are all resident, else the resident count; a multiple of the period of the rows'
+// alignment either way, so that all rows of a CTA are aligned alike.  Never more than
+// kVRowPartialsPerSm partial rows (one per group) per SM.
+constexpr int kVRowPartialsPerSm = 16;
+int64_t vrow_ctas(const DeviceState& dev, int64_t rows, int groups, int64_t resident, int period) {
+  resident = std::min<int64_t>(resident, (int64_t)dev.sm_count * kVRowPartialsPerSm / groups);
+  const int64_t want = (rows + groups - 1) / groups;
+  if (want <= resident / period * period) return (want + period - 1) / period * period;
   return resident / period * period;
 }
 
@@ -306,18 +310,21 @@ int64_t vrow_ctas(int64_t rows, int64_t resident, int period) {
 int launch_vrow_fwd(DeviceState& dev, const DTypeKernels* k, int op, FwdParams& p, int es, cudaStream_t stream, bool* done) {
   *done = false;
   if (p.N <= kWarpRowSizes[2] || !same_phase(p.x, p.x_stride, p.y, p.y_stride, es)) return B200NORM_OK;
-  size_t smem;
-  const int slots = vrow_slots(p.N, es, 1, 2, p.w_dtype, &smem);
-  const int shape = (int64_t)p.N * es / 16 <= kVRowSplit ? 0 : 1;
+  int shape = 0;
+  while (shape < kVRowFwdCount && kVRowFwd[shape].capacity() < (int64_t)p.N * es / 16) ++shape;
+  if (shape == kVRowFwdCount || k->fwd_vrows[op][shape] == nullptr) return B200NORM_OK;
+  const VRowShape& sh = kVRowFwd[shape];
   const void* fn = k->fwd_vrows[op][shape];
-  if (slots == 0 || fn == nullptr) return B200NORM_OK;
+  size_t smem;
+  const int slots = vrow_slots(p.N, es, sh.groups, 2, p.w_dtype, &smem);
+  if (slots == 0) return B200NORM_OK;
   int occ;
-  if (int rc = occupancy(dev, fn, kRowThreads[shape], smem, &occ)) return rc;
-  const int64_t grid = vrow_ctas(p.M, (int64_t)dev.sm_count * occ, phase_period(p.x_stride, es));
+  if (int rc = occupancy(dev, fn, sh.threads(), smem, &occ)) return rc;
+  const int64_t grid = vrow_ctas(dev, p.M, sh.groups, (int64_t)dev.sm_count * occ, phase_period(p.x_stride, es));
   if (grid < 1) return B200NORM_OK;
   p.V = slots;
   *done = true;
-  return launch(fn, dim3(static_cast<unsigned>(grid)), dim3(kRowThreads[shape]), smem, &p, stream, false);
+  return launch(fn, dim3(static_cast<unsigned>(grid)), dim3(sh.threads()), smem, &p, stream, false);
 }
 
 int check_common(int64_t M, int64_t N, int io_dtype, int w_dtype) {
@@ -381,7 +388,7 @@ struct BwdPlan {
   int ctas_per_shard;
   size_t smem;
   const void* vrow;  // any alignment: the vector row kernel (dx and partial rows in one), or null
-  int vrow_threads, vrow_slots;
+  int vrow_threads, vrow_groups, vrow_slots;
 };
 
 // The buffers of a backward call, for the choice among the any-alignment kernels.
@@ -391,9 +398,10 @@ struct BwdBuffers {
   int w_dtype;
 };
 
-// Upper bound of the partial rows per shard of a vector row kernel (256 threads, 2048 per SM).
-int64_t vrow_ctas_bound(const DeviceState& dev, int64_t rows_per_shard) {
-  return std::min<int64_t>(rows_per_shard, (int64_t)dev.sm_count * 8);
+// Upper bound of the partial rows per shard of a vector row kernel: one per row group, the CTA count
+// rounded up to at most 8 more (the period of the rows' alignment).
+int64_t vrow_partials_bound(const DeviceState& dev, int64_t rows_per_shard) {
+  return std::min<int64_t>(rows_per_shard + 64, (int64_t)dev.sm_count * kVRowPartialsPerSm);
 }
 
 // Partial rows per shard of the any-alignment dweight / dbias kernel (one thread per column, one CTA
@@ -416,21 +424,24 @@ int plan_bwd(DeviceState& dev, const DTypeKernels* k, int op, int64_t rows_per_s
     if (bufs == nullptr || act != 0 || rows_per_shard < 1 || N <= kWarpRowSizes[2] ||
         !same_phase(bufs->x, bufs->xs, bufs->dy, bufs->dys, es) || !same_phase(bufs->x, bufs->xs, bufs->dx, bufs->dxs, es))
       return B200NORM_OK;
-    size_t smem;
-    const int slots = vrow_slots(N, es, 2, 1, bufs->w_dtype, &smem);
-    if (slots == 0) return B200NORM_OK;
-    for (int i = 0; i < kVRowShapeCount; ++i) {
+    for (int i = 0; i < kVRowBwdCount; ++i) {
+      const VRowShape& sh = kVRowBwd[i];
       const void* fn = k->bwd_vrows[op][i];
-      if (fn == nullptr || (int64_t)kVRowShapes[i].threads * kVRowShapes[i].packets < N * es / 16) continue;
+      if (fn == nullptr || sh.capacity() < N * es / 16) continue;
+      size_t smem;
+      const int slots = vrow_slots(N, es, 2 * sh.groups, 1, bufs->w_dtype, &smem);
+      if (slots == 0) return B200NORM_OK;
       int occ;
-      if (int rc = occupancy(dev, fn, kVRowShapes[i].threads, smem, &occ)) return rc;
-      const int64_t ctas = vrow_ctas(rows_per_shard, (int64_t)dev.sm_count * occ, phase_period(bufs->xs, es));
-      if (ctas < 1 || ctas > vrow_ctas_bound(dev, rows_per_shard)) return B200NORM_OK;
+      if (int rc = occupancy(dev, fn, sh.threads(), smem, &occ)) return rc;
+      const int64_t ctas =
+          vrow_ctas(dev, rows_per_shard, sh.groups, (int64_t)dev.sm_count * occ, phase_period(bufs->xs, es));
+      if (ctas < 1) return B200NORM_OK;
       plan->vrow = fn;
-      plan->vrow_threads = kVRowShapes[i].threads;
+      plan->vrow_threads = sh.threads();
+      plan->vrow_groups = sh.groups;
       plan->vrow_slots = slots;
       plan->smem = smem;
-      plan->ctas_per_shard = static_cast<int>(ctas);
+      plan->ctas_per_shard = static_cast<int>(ctas * sh.groups);  // partial rows: one per row group
       return B200NORM_OK;
     }
     return B200NORM_OK;
@@ -555,7 +566,8 @@ int bwd_impl(int op, const void* x, int64_t xs, const void* dy, int64_t dys, con
       return rc;
   } else if (plan.vrow != nullptr) {
     p.V = plan.vrow_slots;
-    if (int rc = launch(plan.vrow, dim3(static_cast<unsigned>(P)), dim3(plan.vrow_threads), plan.smem, &p, stream, false))
+    if (int rc = launch(plan.vrow, dim3(static_cast<unsigned>(P / plan.vrow_groups)), dim3(plan.vrow_threads), plan.smem, &p,
+                        stream, false))
       return rc;
   } else {
     if (M > 0) {
@@ -883,7 +895,7 @@ size_t b200norm_bwd_workspace_bytes(int64_t M, int64_t N, int io_dtype, int row_
   const DTypeKernels* k = kernels_for(io_dtype);
   const int64_t rps = M / row_shards;
   int64_t per_shard = any_ctas_per_shard(rps, N);
-  if (N > kWarpRowSizes[2]) per_shard = std::max(per_shard, vrow_ctas_bound(*dev, rps));  // misaligned views of any N
+  if (N > kWarpRowSizes[2]) per_shard = std::max(per_shard, vrow_partials_bound(*dev, rps));  // misaligned views of any N
   if ((N * k->elem_size) % 16 == 0) {
     // LayerNorm and RMSNorm instantiations may differ in occupancy: take the larger.
     // and with or without a fused activation

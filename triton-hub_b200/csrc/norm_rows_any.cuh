@@ -241,6 +241,7 @@ __global__ void __launch_bounds__(THREADS) norm_fwd_row_kernel(const FwdParams p
       }
     }
     stage_row_out<T>(s_out, yrow, N, tid, THREADS);
+    if (stages == 1) __syncthreads();  // the edge elements other threads just wrote into the only slot
   }
   if (tid == 0 && cta_abort) linger_after_abort();
 }
@@ -341,6 +342,7 @@ __global__ void __launch_bounds__(THREADS) norm_bwd_dx_row_kernel(const BwdParam
       }
     }
     stage_row_out<T>(s_out, dxrow, N, tid, THREADS);
+    if (stages == 1) __syncthreads();  // the edge elements other threads just wrote into the only slot
   }
   if (tid == 0 && cta_abort) linger_after_abort();
 }
@@ -408,13 +410,13 @@ __device__ __forceinline__ float param_scalar(const void* p, int dtype, int c, f
 }
 
 // The output pass of the forward kernel over the interior packets of one row.
-template <typename T, typename P, int THREADS, bool HAS_W, bool HAS_B>
+template <typename T, typename P, int GT, bool HAS_W, bool HAS_B>
 __device__ __forceinline__ void vrow_fwd_out(const uint4* xs4, const unsigned char* s_w, const unsigned char* s_b,
-                                             uint4* ybody, int VB, int tid, float mean, float rstd) {
+                                             uint4* ybody, int VB, int gtid, float mean, float rstd) {
   constexpr int EPP = Pack16<T>::kElems, H = EPP / 2;
   const float2 nm = splat2(-mean), rs = splat2(rstd);
 #pragma unroll 2
-  for (int v = tid; v < VB; v += THREADS) {
+  for (int v = gtid; v < VB; v += GT) {
     float2 f[H], w[H], b[H];
     Pack16<T>::unpack2(xs4[v], f);
     if (HAS_W) ld_param_chunk<P, EPP>(s_w, v, w);
@@ -430,61 +432,67 @@ __device__ __forceinline__ void vrow_fwd_out(const uint4* xs4, const unsigned ch
     st_stream(ybody + v, Pack16<T>::pack2(f));
   }
 }
-template <typename T, typename P, int THREADS>
+template <typename T, typename P, int GT>
 __device__ __forceinline__ void vrow_fwd_out_any(bool has_w, bool has_b, const uint4* xs4, const unsigned char* s_w,
-                                                 const unsigned char* s_b, uint4* ybody, int VB, int tid, float mean,
+                                                 const unsigned char* s_b, uint4* ybody, int VB, int gtid, float mean,
                                                  float rstd) {
-  if (has_w && has_b) vrow_fwd_out<T, P, THREADS, true, true>(xs4, s_w, s_b, ybody, VB, tid, mean, rstd);
-  else if (has_w) vrow_fwd_out<T, P, THREADS, true, false>(xs4, s_w, s_b, ybody, VB, tid, mean, rstd);
-  else if (has_b) vrow_fwd_out<T, P, THREADS, false, true>(xs4, s_w, s_b, ybody, VB, tid, mean, rstd);
-  else vrow_fwd_out<T, P, THREADS, false, false>(xs4, s_w, s_b, ybody, VB, tid, mean, rstd);
+  if (has_w && has_b) vrow_fwd_out<T, P, GT, true, true>(xs4, s_w, s_b, ybody, VB, gtid, mean, rstd);
+  else if (has_w) vrow_fwd_out<T, P, GT, true, false>(xs4, s_w, s_b, ybody, VB, gtid, mean, rstd);
+  else if (has_b) vrow_fwd_out<T, P, GT, false, true>(xs4, s_w, s_b, ybody, VB, gtid, mean, rstd);
+  else vrow_fwd_out<T, P, GT, false, false>(xs4, s_w, s_b, ybody, VB, gtid, mean, rstd);
 }
 
-template <typename T, int THREADS, bool RMS>
-__global__ void __launch_bounds__(THREADS) norm_fwd_vrow_kernel(const FwdParams p) {
-  constexpr int WARPS = THREADS / 32;
+// A CTA is WARPS_M row groups of WARPS_N warps; each group works on a row of its own, with its own
+// ring of slots, and the groups share the CTA's copy of the parameter vectors.  Group g of CTA c
+// takes rows c + (g + i * WARPS_M) * gridDim.x, i = 0, 1, ...
+template <typename T, int WARPS_M, int WARPS_N, bool RMS>
+__global__ void __launch_bounds__(32 * WARPS_M * WARPS_N) norm_fwd_vrow_kernel(const FwdParams p) {
+  constexpr int GT = 32 * WARPS_N, THREADS = GT * WARPS_M;
   constexpr int ES = static_cast<int>(sizeof(T)), EPP = Pack16<T>::kElems, H = EPP / 2;
   extern __shared__ __align__(128) unsigned char dyn_smem[];
-  __shared__ float red[2 * WARPS];
-  __shared__ __align__(8) uint64_t full_bar[kRowStagesMax];
+  __shared__ float red[WARPS_M][2 * WARPS_N];
+  __shared__ __align__(8) uint64_t full_bar[WARPS_M][kRowStagesMax];
   __shared__ int cta_abort;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int warp_m = warp / WARPS_N, warp_n = warp - warp_m * WARPS_N, gtid = tid - warp_m * GT;
   const int N = p.N, stages = p.V;
   const size_t slot_bytes = vrow_interior_bytes(N, ES);
   const T* xb = static_cast<const T*>(p.x);
   T* yb = static_cast<T*>(p.y);
-  const int64_t row0 = blockIdx.x, step = gridDim.x;
+  const int64_t row0 = blockIdx.x + (int64_t)warp_m * gridDim.x, step = (int64_t)WARPS_M * gridDim.x;
   // the same for every row of this CTA
-  const RowSpan<T> sp(xb + row0 * p.x_stride, N);
+  const RowSpan<T> sp(xb + (int64_t)blockIdx.x * p.x_stride, N);
   const int VB = sp.body_bytes / 16;
   const int edges = sp.head + (N - sp.tail0);
-  unsigned char* s_w = dyn_smem + (size_t)stages * slot_bytes;
+  unsigned char* ring = dyn_smem + (size_t)warp_m * stages * slot_bytes;
+  unsigned char* s_w = dyn_smem + (size_t)WARPS_M * stages * slot_bytes;
   unsigned char* s_b = s_w + vrow_param_bytes(N, p.w_dtype);
   const bool has_w = p.w != nullptr, has_b = !RMS && p.b != nullptr;
   int phase_bit = 0;
 
-  auto fill = [&](int slot, int64_t row) {  // the leader only
-    mbar_expect_tx(&full_bar[slot], static_cast<uint32_t>(sp.body_bytes));
-    bulk_load(dyn_smem + (size_t)slot * slot_bytes, xb + row * p.x_stride + sp.head, static_cast<uint32_t>(sp.body_bytes),
-              &full_bar[slot]);
+  auto fill = [&](int slot, int64_t row) {  // the group's leader only
+    mbar_expect_tx(&full_bar[warp_m][slot], static_cast<uint32_t>(sp.body_bytes));
+    bulk_load(ring + (size_t)slot * slot_bytes, xb + row * p.x_stride + sp.head, static_cast<uint32_t>(sp.body_bytes),
+              &full_bar[warp_m][slot]);
   };
 
-  if (tid == 0) {
-    for (int i = 0; i < kRowStagesMax; ++i) mbar_init(&full_bar[i], 1);
-    cta_abort = 0;
+  if (tid == 0) cta_abort = 0;
+  if (gtid == 0) {
+    for (int i = 0; i < kRowStagesMax; ++i) mbar_init(&full_bar[warp_m][i], 1);
     mbar_init_fence();
     for (int s = 0; s < stages; ++s) {
       const int64_t r = row0 + (int64_t)s * step;
       if (r < p.M) fill(s, r);
     }
   }
-  // this thread's edge element, if it has one
-  const int ej = tid - (THREADS - 32);
-  const bool is_edge = ej >= 0 && ej < edges;
+  // this thread's edge element, if it has one: the group's last warp holds them
+  const int ej = gtid - (GT - 32);
+  const bool is_edge = ej >= 0 && ej < edges && row0 < p.M;
   const int ecol = is_edge ? (ej < sp.head ? ej : sp.tail0 + (ej - sp.head)) : 0;
   float xe_next = 0.f, we = 1.f, be = 0.f;
+  const T* xe_ptr = xb + row0 * p.x_stride + ecol;
   if (is_edge) {
-    xe_next = to_f32(xb[row0 * p.x_stride + ecol]);
+    xe_next = to_f32(*xe_ptr);
     we = param_scalar(p.w, p.w_dtype, ecol, 1.f);
     be = RMS ? 0.f : param_scalar(p.b, p.w_dtype, ecol, 0.f);
   }
@@ -493,32 +501,34 @@ __global__ void __launch_bounds__(THREADS) norm_fwd_vrow_kernel(const FwdParams 
   __syncthreads();  // barriers initialised, parameters in place
 
   const float inv_n = 1.f / static_cast<float>(N);
+  const int64_t xe_step = step * p.x_stride;
   int slot = 0, prev_slot = -1;
   uint32_t parity = 0;
   for (int64_t row = row0; row < p.M; row += step) {
     const float xe = xe_next;
-    if (is_edge && row + step < p.M) xe_next = to_f32(xb[(row + step) * p.x_stride + ecol]);
-    mbar_wait(&full_bar[slot], parity, &cta_abort, p.status);
-    const uint4* xs4 = reinterpret_cast<const uint4*>(dyn_smem + (size_t)slot * slot_bytes);
+    xe_ptr += xe_step;
+    if (is_edge && row + step < p.M) xe_next = to_f32(*xe_ptr);
+    mbar_wait(&full_bar[warp_m][slot], parity, &cta_abort, p.status);
+    const uint4* xs4 = reinterpret_cast<const uint4*>(ring + (size_t)slot * slot_bytes);
     float mean = 0.f;
     if (!RMS) {
       float2 a = splat2(0.f);
 #pragma unroll 4
-      for (int v = tid; v < VB; v += THREADS) {
+      for (int v = gtid; v < VB; v += GT) {
         float2 f[H];
         Pack16<T>::unpack2(xs4[v], f);
 #pragma unroll
         for (int h = 0; h < H; ++h) a = add2(a, f[h]);
       }
       float s[1] = {a.x + a.y + (is_edge ? xe : 0.f)};
-      group_sum<WARPS, 1, 0>(s, red, phase_bit, 0, warp, lane);
+      group_sum<WARPS_N, 1>(s, red[warp_m], phase_bit, warp_m, warp_n, lane);
       mean = s[0] * inv_n;
     }
     float2 q2 = splat2(0.f);
     {
       const float2 nm = splat2(-mean);
 #pragma unroll 4
-      for (int v = tid; v < VB; v += THREADS) {
+      for (int v = gtid; v < VB; v += GT) {
         float2 f[H];
         Pack16<T>::unpack2(xs4[v], f);
 #pragma unroll
@@ -529,26 +539,28 @@ __global__ void __launch_bounds__(THREADS) norm_fwd_vrow_kernel(const FwdParams 
       }
     }
     float q[1] = {q2.x + q2.y + (is_edge ? (xe - mean) * (xe - mean) : 0.f)};
-    group_sum<WARPS, 1, 0>(q, red, phase_bit, 0, warp, lane);
-    // every thread is past the previous row's output pass: its slot can take the row `stages` on
-    if (tid == 0 && prev_slot >= 0) {
+    group_sum<WARPS_N, 1>(q, red[warp_m], phase_bit, warp_m, warp_n, lane);
+    // every thread of the group is past the previous row's output pass: its slot can take the row
+    // `stages` on
+    if (gtid == 0 && prev_slot >= 0) {
       const int64_t r = row + (int64_t)(stages - 1) * step;
       if (r < p.M) fill(prev_slot, r);
     }
     const float rstd = 1.f / sqrtf(q[0] * inv_n + p.eps);
-    if (tid == 0) {
+    if (gtid == 0) {
       if (!RMS) p.mean[row] = mean;
       p.rstd[row] = rstd;
     }
     T* yrow = yb + row * p.y_stride;
     uint4* ybody = reinterpret_cast<uint4*>(yrow + sp.head);
     switch (p.w_dtype) {
-      case kF32: vrow_fwd_out_any<T, float, THREADS>(has_w, has_b, xs4, s_w, s_b, ybody, VB, tid, mean, rstd); break;
-      case kF16: vrow_fwd_out_any<T, __half, THREADS>(has_w, has_b, xs4, s_w, s_b, ybody, VB, tid, mean, rstd); break;
-      case kBF16: vrow_fwd_out_any<T, __nv_bfloat16, THREADS>(has_w, has_b, xs4, s_w, s_b, ybody, VB, tid, mean, rstd); break;
-      default: vrow_fwd_out_any<T, double, THREADS>(has_w, has_b, xs4, s_w, s_b, ybody, VB, tid, mean, rstd); break;
+      case kF32: vrow_fwd_out_any<T, float, GT>(has_w, has_b, xs4, s_w, s_b, ybody, VB, gtid, mean, rstd); break;
+      case kF16: vrow_fwd_out_any<T, __half, GT>(has_w, has_b, xs4, s_w, s_b, ybody, VB, gtid, mean, rstd); break;
+      case kBF16: vrow_fwd_out_any<T, __nv_bfloat16, GT>(has_w, has_b, xs4, s_w, s_b, ybody, VB, gtid, mean, rstd); break;
+      default: vrow_fwd_out_any<T, double, GT>(has_w, has_b, xs4, s_w, s_b, ybody, VB, gtid, mean, rstd); break;
     }
     if (is_edge) yrow[ecol] = from_f32<T>((xe - mean) * rstd * we + be);
+    if (WARPS_N == 1) __syncwarp();  // the refill above relies on the group having finished this row
     prev_slot = slot;
     if (++slot == stages) {
       slot = 0;
@@ -559,15 +571,15 @@ __global__ void __launch_bounds__(THREADS) norm_fwd_vrow_kernel(const FwdParams 
 }
 
 // The two passes of the backward kernel over the interior packets of one row.
-template <typename T, typename P, int THREADS, int K, bool RMS, bool HAS_W>
-__device__ __forceinline__ void vrow_bwd_sums(const uint4* xs4, const uint4* gs4, const unsigned char* s_w, int VB, int tid,
+template <typename T, typename P, int GT, int K, bool RMS, bool HAS_W>
+__device__ __forceinline__ void vrow_bwd_sums(const uint4* xs4, const uint4* gs4, const unsigned char* s_w, int VB, int gtid,
                                               float mu, float rs, float2 (&acc_w)[K][Pack16<T>::kElems / 2],
                                               float2 (&acc_b)[K][Pack16<T>::kElems / 2], float2& s0, float2& s1) {
   constexpr int EPP = Pack16<T>::kElems, H = EPP / 2;
   const float2 nm = splat2(-mu), r2 = splat2(rs);
 #pragma unroll
   for (int k = 0; k < K; ++k) {
-    const int v = tid + k * THREADS;
+    const int v = gtid + k * GT;
     if (v < VB) {
       float2 x[H], g[H], w[H];
       Pack16<T>::unpack2(xs4[v], x);
@@ -585,14 +597,14 @@ __device__ __forceinline__ void vrow_bwd_sums(const uint4* xs4, const uint4* gs4
     }
   }
 }
-template <typename T, typename P, int THREADS, int K, bool RMS, bool HAS_W>
+template <typename T, typename P, int GT, int K, bool RMS, bool HAS_W>
 __device__ __forceinline__ void vrow_bwd_dx(const uint4* xs4, const uint4* gs4, const unsigned char* s_w, uint4* dxbody,
-                                            int VB, int tid, float mu, float rs, float c1, float c2) {
+                                            int VB, int gtid, float mu, float rs, float c1, float c2) {
   constexpr int EPP = Pack16<T>::kElems, H = EPP / 2;
   const float2 nm = splat2(-mu), r2 = splat2(rs), nc1 = splat2(-c1), nc2 = splat2(-c2);
 #pragma unroll
   for (int k = 0; k < K; ++k) {
-    const int v = tid + k * THREADS;
+    const int v = gtid + k * GT;
     if (v < VB) {
       float2 x[H], g[H], w[H];
       Pack16<T>::unpack2(xs4[v], x);
@@ -609,69 +621,83 @@ __device__ __forceinline__ void vrow_bwd_dx(const uint4* xs4, const uint4* gs4, 
   }
 }
 
-template <typename T, int THREADS, int K, bool RMS>
-__global__ void __launch_bounds__(THREADS) norm_bwd_vrow_kernel(const BwdParams p) {
-  constexpr int WARPS = THREADS / 32;
+// Backward: row groups as in the forward kernel, within a row shard -- CTA c of the shard's
+// p.ctas_per_shard / WARPS_M serves rows c + (g + i * WARPS_M) * that count of the shard -- and one
+// partial row of dweight / dbias per group (p.ctas_per_shard counts partial rows), each thread
+// carrying the sums of its K interior packets (and its edge element) across the group's rows.
+template <typename T, int WARPS_M, int WARPS_N, int K, bool RMS>
+__global__ void __launch_bounds__(32 * WARPS_M * WARPS_N, 512 / (32 * WARPS_M * WARPS_N)) norm_bwd_vrow_kernel(const BwdParams p) {
+  constexpr int GT = 32 * WARPS_N, THREADS = GT * WARPS_M;
   constexpr int NV = RMS ? 1 : 2;
   constexpr int ES = static_cast<int>(sizeof(T)), EPP = Pack16<T>::kElems, H = EPP / 2;
   extern __shared__ __align__(128) unsigned char dyn_smem[];
-  __shared__ float red[2 * NV * WARPS];
-  __shared__ __align__(8) uint64_t full_bar[kRowStagesMax];
+  __shared__ float red[WARPS_M][2 * NV * WARPS_N];
+  __shared__ __align__(8) uint64_t full_bar[WARPS_M][kRowStagesMax];
   __shared__ int cta_abort;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int warp_m = warp / WARPS_N, warp_n = warp - warp_m * WARPS_N, gtid = tid - warp_m * GT;
   const int N = p.N, stages = p.V;
   const size_t slot_bytes = vrow_interior_bytes(N, ES);
   const T* xb = static_cast<const T*>(p.x);
   const T* gb = static_cast<const T*>(p.dy);
   T* db = static_cast<T*>(p.dx);
-  // row shards as in the packet kernels: CTA c serves shard c / ctas_per_shard, rows strided by ctas_per_shard
-  const int shard = blockIdx.x / p.ctas_per_shard;
+  const int ctas = p.ctas_per_shard / WARPS_M;  // per shard
+  const int shard = blockIdx.x / ctas, cta = blockIdx.x - shard * ctas;
   const int64_t shard_begin = (int64_t)shard * p.rows_per_shard;
   const int64_t shard_end = min(shard_begin + p.rows_per_shard, p.M);
-  const int64_t row0 = shard_begin + (blockIdx.x - shard * p.ctas_per_shard), step = p.ctas_per_shard;
-  float* dw_row = p.dw_part != nullptr ? p.dw_part + (size_t)blockIdx.x * N : nullptr;
-  float* db_row = (!RMS && p.db_part != nullptr) ? p.db_part + (size_t)blockIdx.x * N : nullptr;
-  if (row0 >= shard_end) {  // no row for this CTA: its partial rows are zero
-    for (int c = tid; c < N; c += THREADS) {
+  const int64_t row0 = shard_begin + cta + (int64_t)warp_m * ctas, step = (int64_t)WARPS_M * ctas;
+  const size_t part = ((size_t)shard * p.ctas_per_shard + (size_t)cta * WARPS_M + warp_m) * N;
+  float* dw_row = p.dw_part != nullptr ? p.dw_part + part : nullptr;
+  float* db_row = (!RMS && p.db_part != nullptr) ? p.db_part + part : nullptr;
+  const bool has_rows = row0 < shard_end;
+  if (shard_begin + cta >= shard_end) {  // no row for this CTA: its partial rows are zero
+    for (int c = gtid; c < N; c += GT) {
       if (dw_row != nullptr) dw_row[c] = 0.f;
       if (db_row != nullptr) db_row[c] = 0.f;
     }
     return;
   }
-  const RowSpan<T> sp(xb + row0 * p.x_stride, N);
+  // the same for every row of this CTA
+  const RowSpan<T> sp(xb + (shard_begin + cta) * p.x_stride, N);
   const int VB = sp.body_bytes / 16;
   const int edges = sp.head + (N - sp.tail0);
-  unsigned char* s_w = dyn_smem + (size_t)(2 * stages) * slot_bytes;
+  unsigned char* ring = dyn_smem + (size_t)warp_m * 2 * stages * slot_bytes;
+  unsigned char* s_w = dyn_smem + (size_t)WARPS_M * 2 * stages * slot_bytes;
   const bool has_w = p.w != nullptr;
   int phase_bit = 0;
 
-  auto fill = [&](int slot, int64_t row) {  // the leader only
-    mbar_expect_tx(&full_bar[slot], static_cast<uint32_t>(2 * sp.body_bytes));
-    unsigned char* shx = dyn_smem + (size_t)(2 * slot) * slot_bytes;
-    bulk_load(shx, xb + row * p.x_stride + sp.head, static_cast<uint32_t>(sp.body_bytes), &full_bar[slot]);
-    bulk_load(shx + slot_bytes, gb + row * p.dy_stride + sp.head, static_cast<uint32_t>(sp.body_bytes), &full_bar[slot]);
+  auto fill = [&](int slot, int64_t row) {  // the group's leader only
+    mbar_expect_tx(&full_bar[warp_m][slot], static_cast<uint32_t>(2 * sp.body_bytes));
+    unsigned char* shx = ring + (size_t)(2 * slot) * slot_bytes;
+    bulk_load(shx, xb + row * p.x_stride + sp.head, static_cast<uint32_t>(sp.body_bytes), &full_bar[warp_m][slot]);
+    bulk_load(shx + slot_bytes, gb + row * p.dy_stride + sp.head, static_cast<uint32_t>(sp.body_bytes),
+              &full_bar[warp_m][slot]);
   };
 
-  if (tid == 0) {
-    for (int i = 0; i < kRowStagesMax; ++i) mbar_init(&full_bar[i], 1);
-    cta_abort = 0;
+  if (tid == 0) cta_abort = 0;
+  if (gtid == 0) {
+    for (int i = 0; i < kRowStagesMax; ++i) mbar_init(&full_bar[warp_m][i], 1);
     mbar_init_fence();
     for (int s = 0; s < stages; ++s) {
       const int64_t r = row0 + (int64_t)s * step;
       if (r < shard_end) fill(s, r);
     }
   }
-  const int ej = tid - (THREADS - 32);
+  const int ej = gtid - (GT - 32);
   const bool is_edge = ej >= 0 && ej < edges;
   const int ecol = is_edge ? (ej < sp.head ? ej : sp.tail0 + (ej - sp.head)) : 0;
-  float xe_next = 0.f, ge_next = 0.f, we = 1.f;
-  if (is_edge) {
-    xe_next = to_f32(xb[row0 * p.x_stride + ecol]);
-    ge_next = to_f32(gb[row0 * p.dy_stride + ecol]);
-    we = param_scalar(p.w, p.w_dtype, ecol, 1.f);
+  float xe_next = 0.f, ge_next = 0.f, we = 1.f, mu_next = 0.f, rs_next = 0.f;
+  const T* xe_ptr = xb + row0 * p.x_stride + ecol;
+  const T* ge_ptr = gb + row0 * p.dy_stride + ecol;
+  if (has_rows) {
+    if (is_edge) {
+      xe_next = to_f32(*xe_ptr);
+      ge_next = to_f32(*ge_ptr);
+      we = param_scalar(p.w, p.w_dtype, ecol, 1.f);
+    }
+    if (!RMS) mu_next = __ldg(p.mean + row0);
+    rs_next = __ldg(p.rstd + row0);
   }
-  float mu_next = RMS ? 0.f : __ldg(p.mean + row0);
-  float rs_next = __ldg(p.rstd + row0);
   if (has_w) stage_params(s_w, p.w, sp.head, VB * EPP, p.w_dtype, tid, THREADS);
   __syncthreads();  // barriers initialised, weight in place
 
@@ -682,25 +708,28 @@ __global__ void __launch_bounds__(THREADS) norm_bwd_vrow_kernel(const BwdParams 
     for (int h = 0; h < H; ++h) acc_w[k][h] = acc_b[k][h] = splat2(0.f);
   float ew_acc = 0.f, eb_acc = 0.f;
   const float inv_n = 1.f / static_cast<float>(N);
+  const int64_t xe_step = step * p.x_stride, ge_step = step * p.dy_stride;
   int slot = 0, prev_slot = -1;
   uint32_t parity = 0;
   for (int64_t row = row0; row < shard_end; row += step) {
     const float xe = xe_next, ge = ge_next, mu = mu_next, rs = rs_next;
+    xe_ptr += xe_step;
+    ge_ptr += ge_step;
     if (row + step < shard_end) {
       if (is_edge) {
-        xe_next = to_f32(xb[(row + step) * p.x_stride + ecol]);
-        ge_next = to_f32(gb[(row + step) * p.dy_stride + ecol]);
+        xe_next = to_f32(*xe_ptr);
+        ge_next = to_f32(*ge_ptr);
       }
       if (!RMS) mu_next = __ldg(p.mean + row + step);
       rs_next = __ldg(p.rstd + row + step);
     }
-    mbar_wait(&full_bar[slot], parity, &cta_abort, p.status);
-    const uint4* xs4 = reinterpret_cast<const uint4*>(dyn_smem + (size_t)(2 * slot) * slot_bytes);
-    const uint4* gs4 = reinterpret_cast<const uint4*>(dyn_smem + (size_t)(2 * slot + 1) * slot_bytes);
+    mbar_wait(&full_bar[warp_m][slot], parity, &cta_abort, p.status);
+    const uint4* xs4 = reinterpret_cast<const uint4*>(ring + (size_t)(2 * slot) * slot_bytes);
+    const uint4* gs4 = reinterpret_cast<const uint4*>(ring + (size_t)(2 * slot + 1) * slot_bytes);
     float2 s0 = splat2(0.f), s1 = splat2(0.f);
-#define B200NORM_VROW_SUMS(P)                                                                                          \
-  if (has_w) vrow_bwd_sums<T, P, THREADS, K, RMS, true>(xs4, gs4, s_w, VB, tid, mu, rs, acc_w, acc_b, s0, s1);          \
-  else vrow_bwd_sums<T, P, THREADS, K, RMS, false>(xs4, gs4, s_w, VB, tid, mu, rs, acc_w, acc_b, s0, s1)
+#define B200NORM_VROW_SUMS(P)                                                                                   \
+  if (has_w) vrow_bwd_sums<T, P, GT, K, RMS, true>(xs4, gs4, s_w, VB, gtid, mu, rs, acc_w, acc_b, s0, s1);       \
+  else vrow_bwd_sums<T, P, GT, K, RMS, false>(xs4, gs4, s_w, VB, gtid, mu, rs, acc_w, acc_b, s0, s1)
     switch (p.w_dtype) {
       case kF32: B200NORM_VROW_SUMS(float); break;
       case kF16: B200NORM_VROW_SUMS(__half); break;
@@ -720,9 +749,10 @@ __global__ void __launch_bounds__(THREADS) norm_bwd_vrow_kernel(const BwdParams 
       ew_acc += ge * xh_e;
       eb_acc += ge;
     }
-    group_sum<WARPS, NV, 0>(s, red, phase_bit, 0, warp, lane);
-    // every thread is past the previous row's dx pass: its slot can take the row `stages` on
-    if (tid == 0 && prev_slot >= 0) {
+    group_sum<WARPS_N, NV>(s, red[warp_m], phase_bit, warp_m, warp_n, lane);
+    // every thread of the group is past the previous row's dx pass: its slot can take the row
+    // `stages` on
+    if (gtid == 0 && prev_slot >= 0) {
       const int64_t r = row + (int64_t)(stages - 1) * step;
       if (r < shard_end) fill(prev_slot, r);
     }
@@ -730,9 +760,9 @@ __global__ void __launch_bounds__(THREADS) norm_bwd_vrow_kernel(const BwdParams 
     const float c2 = RMS ? 0.f : s[NV - 1] * inv_n;
     T* dxrow = db + row * p.dx_stride;
     uint4* dxbody = reinterpret_cast<uint4*>(dxrow + sp.head);
-#define B200NORM_VROW_DX(P)                                                                                  \
-  if (has_w) vrow_bwd_dx<T, P, THREADS, K, RMS, true>(xs4, gs4, s_w, dxbody, VB, tid, mu, rs, c1, c2);         \
-  else vrow_bwd_dx<T, P, THREADS, K, RMS, false>(xs4, gs4, s_w, dxbody, VB, tid, mu, rs, c1, c2)
+#define B200NORM_VROW_DX(P)                                                                            \
+  if (has_w) vrow_bwd_dx<T, P, GT, K, RMS, true>(xs4, gs4, s_w, dxbody, VB, gtid, mu, rs, c1, c2);       \
+  else vrow_bwd_dx<T, P, GT, K, RMS, false>(xs4, gs4, s_w, dxbody, VB, gtid, mu, rs, c1, c2)
     switch (p.w_dtype) {
       case kF32: B200NORM_VROW_DX(float); break;
       case kF16: B200NORM_VROW_DX(__half); break;
@@ -741,16 +771,17 @@ __global__ void __launch_bounds__(THREADS) norm_bwd_vrow_kernel(const BwdParams 
     }
 #undef B200NORM_VROW_DX
     if (is_edge) dxrow[ecol] = from_f32<T>((wdy_e - (xh_e * c1 + c2)) * rs);
+    if (WARPS_N == 1) __syncwarp();  // the refill above relies on the group having finished this row
     prev_slot = slot;
     if (++slot == stages) {
       slot = 0;
       parity ^= 1u;
     }
   }
-  // this CTA's partial rows
+  // this group's partial rows (all zeros for a group without rows)
 #pragma unroll
   for (int k = 0; k < K; ++k) {
-    const int v = tid + k * THREADS;
+    const int v = gtid + k * GT;
     if (v < VB) {
       const int c = sp.head + v * EPP;
 #pragma unroll

@@ -26,16 +26,20 @@ constexpr int kWarpRowSizes[3] = {256, 512, 1024};  // 32 lanes x 8 / 16 / 32 el
 constexpr int kRowShapeCount = 2;
 constexpr int kRowThreads[kRowShapeCount] = {256, 512};
 constexpr int kRowSplit = 8192;
-// The vector kernels for rows whose buffers share one alignment: forward with kRowThreads threads
-// (up to kVRowSplit interior packets with [0]); backward with kVRowShapes[i].threads threads that each
-// carry dweight / dbias of kVRowShapes[i].packets interior packets (a null entry: no such kernel for
-// this storage type).
-constexpr int kVRowSplit = 1024;
+// The vector kernels for rows whose buffers share one alignment: CTAs of `groups` row groups of `warps`
+// warps each.  Forward: a shape serves rows of up to 32 * warps * kVRowFwdPackets interior packets.
+// Backward: every thread carries dweight / dbias of `packets` interior packets (a null entry in the
+// tables: no such kernel for this storage type).  Ascending capacity.
 struct VRowShape {
-  int threads, packets;
+  int groups, warps, packets;
+  int threads() const { return 32 * groups * warps; }
+  int capacity() const { return 32 * warps * packets; }
 };
-constexpr int kVRowShapeCount = 5;
-constexpr VRowShape kVRowShapes[kVRowShapeCount] = {{256, 1}, {256, 2}, {256, 4}, {512, 4}, {512, 8}};
+constexpr int kVRowFwdPackets = 8;
+constexpr int kVRowFwdCount = 5;
+constexpr VRowShape kVRowFwd[kVRowFwdCount] = {{8, 1, 8}, {4, 2, 8}, {2, 4, 8}, {1, 8, 8}, {1, 16, 8}};
+constexpr int kVRowBwdCount = 6;
+constexpr VRowShape kVRowBwd[kVRowBwdCount] = {{8, 1, 4}, {4, 2, 4}, {2, 4, 4}, {1, 8, 4}, {1, 16, 4}, {1, 16, 8}};
 
 struct DTypeKernels {
   int elem_size;
@@ -52,8 +56,8 @@ struct DTypeKernels {
   const void* fwd_warp_rows[2][3];
   const void* bwd_dx_warp_rows[2][3];
   const void* bwd_dwdb_any[2];
-  const void* fwd_vrows[2][kRowShapeCount];
-  const void* bwd_vrows[2][kVRowShapeCount];
+  const void* fwd_vrows[2][kVRowFwdCount];
+  const void* bwd_vrows[2][kVRowBwdCount];
   const void* act_packet[2];    // stand-alone activation, [0] forward [1] backward (tables of an activation only)
   const void* act_any[2];
 };
