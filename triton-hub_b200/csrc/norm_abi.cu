@@ -283,7 +283,8 @@ int phase_period(int64_t stride, int es) {
 int vrow_slots(int64_t N, int es, int rows_per_slot, int param_vectors, int w_dtype, size_t* smem) {
   const size_t interior = vrow_interior_bytes(N, es) * rows_per_slot;  // of all the CTA's row groups
   const size_t params = vrow_param_bytes(N, w_dtype) * param_vectors;
-  const size_t caps[3] = {72 * 1024, 112 * 1024, kMaxSmemPerCta - 4096};
+  // three, two or one CTA per SM (228 KB, 1 KB of it reserved per CTA, a little static shared memory)
+  const size_t caps[3] = {74 * 1024, 112 * 1024 + 512, kMaxSmemPerCta - 4096};
   for (size_t cap : caps)
     for (int slots = 4; slots >= 2; --slots)
       if (slots * interior + params <= cap) {
