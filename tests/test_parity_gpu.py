@@ -175,7 +175,9 @@ def test_row_strided_and_non_contiguous_inputs():
 @pytest.mark.parametrize("rms", [False, True])
 @pytest.mark.parametrize("dtype,N,M", [("bf16", 4097, 2600), ("bf16", 1025, 3000), ("fp16", 2050, 2400), ("fp32", 1027, 2400),
                                        ("fp32", 4101, 1300), ("fp64", 1031, 1300), ("bf16", 12289, 700),
-                                       ("bf16", 16391, 400), ("fp32", 16383, 400), ("bf16", 20001, 300)])
+                                       ("bf16", 16391, 400), ("fp32", 16383, 400), ("bf16", 20001, 300),
+                                       ("bf16", 513, 3000), ("fp16", 777, 3000), ("fp32", 257, 3000), ("fp32", 1001, 3000),
+                                       ("fp64", 129, 1300), ("bf16", 511, 3000)])
 def test_rows_of_odd_length_in_contiguous_tensors(dtype, N, M, rms):
     """Contiguous rows of an odd length: x, dy, y and dx start every row at the same offset within a
     16-byte line, which the vector row kernels need; more rows than resident CTAs, so that every CTA

@@ -299,6 +299,10 @@ int vrow_slots(int64_t N, int es, int rows_per_slot, int param_vectors, int w_dt
 // alignment either way, so that all rows of a CTA are aligned alike.  Never more than
 // kVRowPartialsPerSm partial rows (one per group) per SM.
 constexpr int kVRowPartialsPerSm = 16;
+// Shorter rows go to the warp-per-row kernels: the vector kernels' per-row bookkeeping outweighs their
+// packets there.  The backward switches earlier, because the warp-per-row path pays for a separate
+// dweight / dbias pass over x and dy.
+constexpr int64_t kVRowMinBytesFwd = 2049, kVRowMinBytesBwd = 1024;
 int64_t vrow_ctas(const DeviceState& dev, int64_t rows, int groups, int64_t resident, int period) {
   resident = std::min<int64_t>(resident, (int64_t)dev.sm_count * kVRowPartialsPerSm / groups);
   const int64_t want = (rows + groups - 1) / groups;
@@ -310,7 +314,7 @@ int64_t vrow_ctas(const DeviceState& dev, int64_t rows, int groups, int64_t resi
 // it was launched.
 int launch_vrow_fwd(DeviceState& dev, const DTypeKernels* k, int op, FwdParams& p, int es, cudaStream_t stream, bool* done) {
   *done = false;
-  if (p.N <= kWarpRowSizes[2] || !same_phase(p.x, p.x_stride, p.y, p.y_stride, es)) return B200NORM_OK;
+  if ((int64_t)p.N * es < kVRowMinBytesFwd || !same_phase(p.x, p.x_stride, p.y, p.y_stride, es)) return B200NORM_OK;
   int shape = 0;
   while (shape < kVRowFwdCount && kVRowFwd[shape].capacity() < (int64_t)p.N * es / 16) ++shape;
   if (shape == kVRowFwdCount || k->fwd_vrows[op][shape] == nullptr) return B200NORM_OK;
@@ -422,7 +426,7 @@ int plan_bwd(DeviceState& dev, const DTypeKernels* k, int op, int64_t rows_per_s
   if (plan->pk == nullptr) {
     plan->ctas_per_shard = any_ctas_per_shard(rows_per_shard, N);
     plan->smem = 0;
-    if (bufs == nullptr || act != 0 || rows_per_shard < 1 || N <= kWarpRowSizes[2] ||
+    if (bufs == nullptr || act != 0 || rows_per_shard < 1 || N * es < kVRowMinBytesBwd ||
         !same_phase(bufs->x, bufs->xs, bufs->dy, bufs->dys, es) || !same_phase(bufs->x, bufs->xs, bufs->dx, bufs->dxs, es))
       return B200NORM_OK;
     for (int i = 0; i < kVRowBwdCount; ++i) {
@@ -896,7 +900,7 @@ size_t b200norm_bwd_workspace_bytes(int64_t M, int64_t N, int io_dtype, int row_
   const DTypeKernels* k = kernels_for(io_dtype);
   const int64_t rps = M / row_shards;
   int64_t per_shard = any_ctas_per_shard(rps, N);
-  if (N > kWarpRowSizes[2]) per_shard = std::max(per_shard, vrow_partials_bound(*dev, rps));  // misaligned views of any N
+  if (N * k->elem_size >= kVRowMinBytesBwd) per_shard = std::max(per_shard, vrow_partials_bound(*dev, rps));  // misaligned views of any N
   if ((N * k->elem_size) % 16 == 0) {
     // LayerNorm and RMSNorm instantiations may differ in occupancy: take the larger.
     // and with or without a fused activation
