@@ -300,9 +300,10 @@ int vrow_slots(int64_t N, int es, int rows_per_slot, int param_vectors, int w_dt
 // kVRowPartialsPerSm partial rows (one per group) per SM.
 constexpr int kVRowPartialsPerSm = 16;
 // Shorter rows go to the warp-per-row kernels: the vector kernels' per-row bookkeeping outweighs their
-// packets there.  The backward switches earlier, because the warp-per-row path pays for a separate
-// dweight / dbias pass over x and dy.
-constexpr int64_t kVRowMinBytesFwd = 2049, kVRowMinBytesBwd = 1024;
+// packets there (measured: 16-bit forward at 1.5 KB per row 0.45 against 0.55 of the copy bandwidth,
+// 32-bit forward at 1.2 KB 0.82).  The backward switches earlier, because the warp-per-row path pays
+// for a separate dweight / dbias pass over x and dy (514-byte rows: 0.33 against 0.18).
+constexpr int64_t kVRowMinBytesFwd16 = 2049, kVRowMinBytesFwd32 = 1024, kVRowMinBytesBwd = 512;
 int64_t vrow_ctas(const DeviceState& dev, int64_t rows, int groups, int64_t resident, int period) {
   resident = std::min<int64_t>(resident, (int64_t)dev.sm_count * kVRowPartialsPerSm / groups);
   const int64_t want = (rows + groups - 1) / groups;
@@ -314,7 +315,7 @@ int64_t vrow_ctas(const DeviceState& dev, int64_t rows, int groups, int64_t resi
 // it was launched.
 int launch_vrow_fwd(DeviceState& dev, const DTypeKernels* k, int op, FwdParams& p, int es, cudaStream_t stream, bool* done) {
   *done = false;
-  if ((int64_t)p.N * es < kVRowMinBytesFwd || !same_phase(p.x, p.x_stride, p.y, p.y_stride, es)) return B200NORM_OK;
+  if ((int64_t)p.N * es < (es >= 4 ? kVRowMinBytesFwd32 : kVRowMinBytesFwd16) || !same_phase(p.x, p.x_stride, p.y, p.y_stride, es)) return B200NORM_OK;
   int shape = 0;
   while (shape < kVRowFwdCount && kVRowFwd[shape].capacity() < (int64_t)p.N * es / 16) ++shape;
   if (shape == kVRowFwdCount || k->fwd_vrows[op][shape] == nullptr) return B200NORM_OK;
