@@ -30,6 +30,13 @@
  *     never allocates.  The first call on a device caches the device's SM count, the
  *     occupancy of each kernel and maps a small pinned status word; make that call before
  *     any stream capture.
+ *   - Alignment.  Any base address, row stride and row length are accepted, like the reference's
+ *     masked loads (layernorm.py:28-46, `cols < N`).  Fastest: every row of every buffer starts on
+ *     a 16-byte boundary and is a multiple of 16 bytes long.  Next: rows of at least 0.5 - 2 KB
+ *     whose buffers are misaligned ALIKE (x, y -- and dy, dx -- start each row at the same offset
+ *     within a 16-byte line: contiguous tensors of an odd row length, views offset by the same
+ *     number of elements); their 16-byte interiors still move and compute as 16-byte packets.
+ *     Everything else runs element by element at a fraction of the bandwidth.
  *   - Arithmetic is fp32 whatever the storage type (the reference promotes every load to
  *     fp32, layernorm.py:31,41); results are rounded once on store.
  *   - Return value: B200NORM_OK or one of the error codes below.  Nothing throws or aborts.
