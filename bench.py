@@ -743,7 +743,7 @@ def run_e2e(wl, x, dy, w, b, rows, world, device, args):
 
     ln = wl["op"] == "ln"
     N, eps, dt = wl["N"], wl["eps"], TDTYPE[wl["dtype"]]
-    pipe = HostPipeline(wl["op"], N, dt, device, eps, w, b)
+    pipe = HostPipeline(wl["op"], N, dt, device, eps, w, b, rows_hint=rows)
     hx, hdy = x.cpu().pin_memory(), dy.cpu().pin_memory()
     hy = torch.empty_like(hx).pin_memory()
     hdx = torch.empty_like(hx).pin_memory()

@@ -27,16 +27,27 @@ class HostPipeline:
 
     op: "ln" or "rms".  weight / bias: device tensors (bias None for RMSNorm or bias-free
     LayerNorm).  chunk_rows rows are in flight per stage; `buffers` device buffer sets rotate.
+    The first chunk's upload and the last chunk's download have nothing to overlap with, so a call
+    of C chunks takes about (C + 1) / C of the bare transfer time: with `rows_hint` (the M the
+    pipeline will be called with) the default chunk is M / 24 rows, kept between 8 and 64 MiB per
+    tensor (smaller chunks would be bound by the host-side launch work per chunk); without it,
+    32 MiB.
     """
 
     def __init__(self, op: str, N: int, dtype: torch.dtype, device, eps: float, weight: Optional[torch.Tensor],
-                 bias: Optional[torch.Tensor] = None, chunk_rows: int = 0, buffers: int = 3):
+                 bias: Optional[torch.Tensor] = None, chunk_rows: int = 0, buffers: int = 3, rows_hint: int = 0):
         assert op in ("ln", "rms")
         self.op, self.N, self.dtype, self.eps = op, N, dtype, eps
         self.device = torch.device(device)
         self.weight, self.bias = weight, (bias if op == "ln" else None)
         esize = torch.empty((), dtype=dtype).element_size()
-        self.chunk_rows = chunk_rows if chunk_rows > 0 else max(256, (32 << 20) // (N * esize))
+        if chunk_rows <= 0:
+            row_bytes = N * esize
+            chunk_bytes = 32 << 20
+            if rows_hint > 0:
+                chunk_bytes = min(64 << 20, max(8 << 20, rows_hint * row_bytes // 24))
+            chunk_rows = max(256, chunk_bytes // row_bytes)
+        self.chunk_rows = chunk_rows
         self.nbuf = buffers
         R = self.chunk_rows
         mk = lambda: torch.empty((R, N), dtype=dtype, device=self.device)
