@@ -430,10 +430,29 @@ int plan_bwd(DeviceState& dev, const DTypeKernels* k, int op, int64_t rows_per_s
     if (bufs == nullptr || act != 0 || rows_per_shard < 1 || N * es < kVRowMinBytesBwd ||
         !same_phase(bufs->x, bufs->xs, bufs->dy, bufs->dys, es) || !same_phase(bufs->x, bufs->xs, bufs->dx, bufs->dxs, es))
       return B200NORM_OK;
+    // The smallest capacity that holds the row.  Among equals, as measured: 16-bit rows of 512 packets or
+    // more do best on eight warps per row (two packets per thread with xhat and w * dy kept beat four
+    // packets on four warps by 15 %, and four packets on eight warps beat two on sixteen by 11 %), shorter
+    // 16-bit rows on fewer warps with more packets each; 32-bit rows do equally well either way and take
+    // the kernel that keeps xhat and w * dy, then more packets per thread.
+    auto better = [&](int i, int b) {
+      const VRowShape &si = kVRowBwd[i], &sb = kVRowBwd[b];
+      if (si.capacity() != sb.capacity()) return si.capacity() < sb.capacity();
+      if (es == 2) {
+        if (si.capacity() >= 512 && (si.warps == 8) != (sb.warps == 8)) return si.warps == 8;
+        return si.packets > sb.packets;
+      }
+      const int vi = k->bwd_vrow_variant[op][i], vb = k->bwd_vrow_variant[op][b];
+      return vi != vb ? vi > vb : si.packets > sb.packets;
+    };
+    int best = -1;
     for (int i = 0; i < kVRowBwdCount; ++i) {
-      const VRowShape& sh = kVRowBwd[i];
-      const void* fn = k->bwd_vrows[op][i];
-      if (fn == nullptr || sh.capacity() < N * es / 16) continue;
+      if (k->bwd_vrows[op][i] == nullptr || kVRowBwd[i].capacity() < N * es / 16) continue;
+      if (best < 0 || better(i, best)) best = i;
+    }
+    if (best >= 0) {
+      const VRowShape& sh = kVRowBwd[best];
+      const void* fn = k->bwd_vrows[op][best];
       size_t smem;
       const int slots = vrow_slots(N, es, 2 * sh.groups, 1, bufs->w_dtype, &smem);
       if (slots == 0) return B200NORM_OK;
@@ -448,7 +467,6 @@ int plan_bwd(DeviceState& dev, const DTypeKernels* k, int op, int64_t rows_per_s
       plan->vrow_slots = slots;
       plan->smem = smem;
       plan->ctas_per_shard = static_cast<int>(ctas * sh.groups);  // partial rows: one per row group
-      return B200NORM_OK;
     }
     return B200NORM_OK;
   }

@@ -28,18 +28,29 @@ constexpr int kRowThreads[kRowShapeCount] = {256, 512};
 constexpr int kRowSplit = 8192;
 // The vector kernels for rows whose buffers share one alignment: CTAs of `groups` row groups of `warps`
 // warps each.  Forward: a shape serves rows of up to 32 * warps * kVRowFwdPackets interior packets.
-// Backward: every thread carries dweight / dbias of `packets` interior packets (a null entry in the
-// tables: no such kernel for this storage type).  Ascending capacity.
+// Backward: every thread carries dweight / dbias of `packets` interior packets; per storage type and op a
+// shape either keeps xhat and w * dy in registers between its two passes, or forms them twice, or does
+// not exist (too many registers), see vrow_bwd_variant().
 struct VRowShape {
   int groups, warps, packets;
-  int threads() const { return 32 * groups * warps; }
-  int capacity() const { return 32 * warps * packets; }
+  constexpr int threads() const { return 32 * groups * warps; }
+  constexpr int capacity() const { return 32 * warps * packets; }
 };
 constexpr int kVRowFwdPackets = 8;
 constexpr int kVRowFwdCount = 5;
 constexpr VRowShape kVRowFwd[kVRowFwdCount] = {{8, 1, 8}, {4, 2, 8}, {2, 4, 8}, {1, 8, 8}, {1, 16, 8}};
-constexpr int kVRowBwdCount = 6;
-constexpr VRowShape kVRowBwd[kVRowBwdCount] = {{8, 1, 4}, {4, 2, 4}, {2, 4, 4}, {1, 8, 4}, {1, 16, 4}, {1, 16, 8}};
+constexpr int kVRowBwdCount = 15;
+constexpr VRowShape kVRowBwd[kVRowBwdCount] = {{8, 1, 2},  {8, 1, 4},  {8, 1, 8},  {4, 2, 2},  {4, 2, 4},
+                                               {4, 2, 8},  {2, 4, 2},  {2, 4, 4},  {2, 4, 8},  {1, 8, 2},
+                                               {1, 8, 4},  {1, 8, 8},  {1, 16, 2}, {1, 16, 4}, {1, 16, 8}};
+// 2: keeps xhat and w * dy (registers for the sums and the kept values: packets * elements per packet *
+// (1 or 2 sums + 2) <= 64: beyond that the 128 registers of a thread spill); 1: forms them twice (sums alone
+// <= 64 registers); 0: no kernel.
+constexpr int vrow_bwd_variant(int packets, int elems_per_packet, bool rms) {
+  const int sums = packets * elems_per_packet * (rms ? 1 : 2);
+  if (sums + packets * elems_per_packet * 2 <= 64) return 2;
+  return sums <= 64 ? 1 : 0;
+}
 
 struct DTypeKernels {
   int elem_size;
@@ -58,6 +69,7 @@ struct DTypeKernels {
   const void* bwd_dwdb_any[2];
   const void* fwd_vrows[2][kVRowFwdCount];
   const void* bwd_vrows[2][kVRowBwdCount];
+  int bwd_vrow_variant[2][kVRowBwdCount];  // vrow_bwd_variant() of each entry
   const void* act_packet[2];    // stand-alone activation, [0] forward [1] backward (tables of an activation only)
   const void* act_any[2];
 };
